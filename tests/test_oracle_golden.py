@@ -1,0 +1,82 @@
+"""The fp32 oracle against known answers produced by the reference's own Triton kernels
+(fixtures made by tests/golden/make_golden.py through the Triton CPU interpreter).
+
+The reference rounds every kernel output to bf16, the oracle does not, so agreement is at the level of
+bf16 rounding of the values involved: a few ulp (2^-8 relative) of the largest magnitudes."""
+import os
+
+import pytest
+import torch
+
+from oracle import vla_oracle as O
+from tests.golden.make_golden import weights_for
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def load(case):
+    path = os.path.join(GOLD, case + ".pt")
+    if not os.path.exists(path):
+        pytest.skip("fixture %s missing" % case)
+    g = torch.load(path)
+    return g, weights_for(case, g["seed"])
+
+
+def close(got, want, rel=2.5e-2, what=""):
+    want = want.float()
+    err = (got - want).abs()
+    scale = want.abs().max().item()
+    assert err.max().item() <= rel * scale, "%s max-abs %.3e vs scale %.3e" % (what, err.max().item(), scale)
+    assert err.mean().item() <= 0.25 * rel * scale, "%s mean-abs %.3e" % (what, err.mean().item())
+
+
+def test_patch_embed():
+    g, w = load("patch_embed")
+    x = O.patchify(w["images"]) @ w["w"].reshape(588, 1152) + w["b"] + w["pos"]
+    close(x[::8], g["vision_x"], what="vision_x")
+
+
+def test_vit_block():
+    g, w = load("vit_block")
+    x, qkv = O.vit_block(w["x"], w["n1w"], w["n1b"], w["qkv_w"], w["qkv_b"], w["o_w"], w["o_b"],
+                         w["n2w"], w["n2b"], w["up_w"], w["up_b"], w["down_w"], w["down_b"])
+    close(qkv[::32], g["qkv"], what="qkv")
+    close(x[::8], g["x_out"], what="x_out")
+
+
+def test_prefix_layer():
+    g, w = load("prefix_layer")
+    cos, sin = O.rope_table(torch.arange(5))
+    x, k, v = O.prefix_layer(w["x"], cos, sin, 5, False, w["qkv_w"], w["o_w"], w["gate_w"], w["up_w"], w["down_w"])
+    close(k, g["K"], what="K")
+    close(v, g["V"], what="V")
+    close(x, g["x_out"], what="x_out")
+
+
+def test_pi0_decoder_layer():
+    g, w = load("pi0_decoder_layer")
+    P, S = 6, 4
+    cos, sin = O.rope_table(torch.arange(S) + P)
+    mask = O.pi0_suffix_mask(P, S)
+    x, k, v = O.pi0_decoder_layer(w["x"], w["K"], w["V"], cos, sin, mask,
+                                  w["qkv_w"], w["o_w"], w["gate_w"], w["up_w"], w["down_w"])
+    close(k, g["K_new"], what="K_new")
+    close(v, g["V_new"], what="V_new")
+    close(x, g["x_out"], what="x_out")
+    # the state token's 8 head rows must put exactly zero weight on keys beyond index P
+    assert g["probs"].float()[:8, P + 1:].abs().max().item() == 0.0
+    assert g["probs"].float()[8:, P + 1:].abs().max().item() > 0.0
+
+
+def test_pi05_decoder_layer():
+    g, w = load("pi05_decoder_layer")
+    PA, PV, S = 7, 5, 4
+    cos, sin = O.rope_table(torch.arange(S) + (PV - 1))
+    mask = torch.ones(S, PA + S, dtype=torch.bool)
+    mask[:, PV:PA] = False
+    x, k, v = O.pi05_decoder_layer(w["x"], w["K"], w["V"], cos, sin, mask, w["style_attn"], w["style_ffn"],
+                                   w["qkv_w"], w["o_w"], w["gate_w"], w["up_w"], w["down_w"])
+    close(k, g["K_new"], what="K_new")
+    close(v, g["V_new"], what="V_new")
+    close(x, g["x_out"], what="x_out")
+    assert g["probs"].float()[:, PV:PA].abs().max().item() == 0.0
