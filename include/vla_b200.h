@@ -1,0 +1,139 @@
+/* C ABI of libvla_b200.so: the Pi0 / Pi05 single-observation forward of realtime-vla on one B200.
+ *
+ * The reference has no native interface: its boundary is the Python object Pi0Inference / Pi05Inference
+ * (pi0_infer.py:1238-1361, pi05_infer.py:530-826).  These entry points are what a Python (ctypes), C or
+ * C++ caller binds to get the same object life cycle without Triton or PyTorch: create -> load the
+ * converted-checkpoint tensors by key -> finalize (builds tables, captures one CUDA graph) -> forward.
+ *
+ * Conventions: every function returns 0 on success and a non-zero vla_error otherwise; nothing throws or
+ * aborts; vla_last_error() gives the message of the last failure on that handle (or of the last failed
+ * vla_create / op call when given NULL).  One handle = one GPU = one stream at a time (not re-entrant,
+ * like the reference object with its static buffers).  The caller owns every pointer it passes in; the
+ * library owns weights, activations and I/O buffers.
+ */
+#ifndef VLA_B200_H
+#define VLA_B200_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct vla_model* vla_handle;
+
+enum vla_error {
+  VLA_OK = 0,
+  VLA_ERR_CUDA = 1,        /* a CUDA runtime/driver call failed */
+  VLA_ERR_KEY = 2,         /* unknown checkpoint key (the reference raises KeyError, pi0_infer.py:1337-1338) */
+  VLA_ERR_SHAPE = 3,       /* shape mismatch (the reference raises RuntimeError from Tensor.copy_) */
+  VLA_ERR_STATE = 4,       /* call out of order (e.g. forward before finalize) */
+  VLA_ERR_LIMIT = 5,       /* size beyond what the kernels support (keys per query > 1024 tokens etc.) */
+  VLA_ERR_DEVICE = 6       /* device-side status word was raised (bounded wait ran out) */
+};
+
+enum vla_model_kind { VLA_PI0 = 0, VLA_PI05 = 1 };
+enum vla_dtype { VLA_BF16 = 0, VLA_F32 = 1 };
+
+/* Mirrors the constructor arguments: Pi0Inference(checkpoint, num_views, chunk_size) (pi0_infer.py:1239),
+ * Pi05Inference(checkpoint, num_views, chunk_size, ..., max_prompt_len) (pi05_infer.py:531-561).
+ * prompt_len is the allocated prompt window: len(checkpoint['language_embeds']) for Pi0 and for Pi05 with
+ * discrete_state_input=False, max_prompt_len otherwise.  Layer/step counts default to the model's
+ * (27 / 18 / 10) when 0; smaller values exist for tests. */
+typedef struct vla_config {
+  int model;          /* vla_model_kind */
+  int num_views;      /* 1..3 camera views of 224x224x3 */
+  int chunk_size;     /* action chunk length */
+  int prompt_len;     /* allocated prompt tokens */
+  int batch;          /* independent observations per forward (1 = the reference's behaviour) */
+  int device;         /* CUDA device ordinal */
+  int n_vit_layers;   /* 0 -> 27 */
+  int n_layers;       /* 0 -> 18 */
+  int n_steps;        /* 0 -> 10 */
+  int flags;          /* bit 0: disable programmatic dependent launch; bit 1: run without a CUDA graph */
+} vla_config;
+
+/* Replaces Pi0Inference.__init__ / Pi05Inference.__init__ up to buffer allocation (pi0_infer.py:1245-1317). */
+int vla_create(const vla_config* cfg, vla_handle* out);
+
+/* Replaces `self.weights[k].copy_(v)` (pi0_infer.py:1337-1338, pi05_infer.py:666-668): `data` is a
+ * contiguous host or device tensor of the checkpoint's shape ([in, out] weights, layers stacked on dim 0),
+ * bf16 or fp32.  The library repacks it into its own layout.  Any subset of keys may be loaded; keys never
+ * loaded stay zero.  'language_embeds' sets the prompt (rows <= prompt_len). */
+int vla_load_weight(vla_handle h, const char* key, const void* data, const int64_t* shape, int ndim, int dtype);
+
+/* Replaces the tail of the constructors: RoPE tables (pi0_infer.py:1319-1335), Pi05 out-projection scaling
+ * and time/style precompute (pi05_infer.py:669-722) and record_infer_graph (pi0_infer.py:1347-1354). */
+int vla_finalize(vla_handle h);
+
+/* Pi05 per-call prompt (pi05_infer.py:819-822): copies `len` rows of bf16 [len,2048] prompt embeddings
+ * (host or device) into the prompt window, sets the valid prefix length and the suffix RoPE start
+ * (num_views*256 + len - 1).  For Pi0 it only replaces the prompt rows (len must equal prompt_len). */
+int vla_set_prompt(vla_handle h, const void* embeds_bf16, int len);
+
+/* Device address and size of a named library-owned buffer, so that a host framework can wrap it without a
+ * copy: "observation_images_normalized" bf16 (batch,nv,224,224,3), "observation_state_normalized" bf16
+ * (batch,32) (Pi0), "diffusion_noise" bf16 (batch,chunk,32) (input noise, overwritten by the actions:
+ * the reference returns this same buffer, pi0_infer.py:1361), plus intermediate buffers used by the tests
+ * ("vision_x", "encoder_x", "encoder_K", "encoder_V", "decoder_x"). */
+int vla_buffer(vla_handle h, const char* name, void** dev_ptr, size_t* bytes);
+
+/* Replaces infer_graph.replay() (pi0_infer.py:1360): runs the forward on `stream` (a cudaStream_t, NULL =
+ * default stream) over the library-owned I/O buffers.  Asynchronous; the caller synchronises. */
+int vla_forward(vla_handle h, void* stream);
+
+/* Replaces Pi0Inference.forward / Pi05Inference.forward for a caller holding HOST memory
+ * (pi0_infer.py:1356-1361): copies bf16 images/state/noise in, runs, copies the bf16 (batch,chunk,32)
+ * actions out and synchronises.  `state` is ignored for Pi05 (may be NULL). */
+int vla_forward_host(vla_handle h, const void* images, const void* state, const void* noise, void* actions_out);
+
+/* Device status word: OR of bounded-wait timeouts / shape violations seen by any kernel (0 = clean). */
+int vla_status_word(vla_handle h, int* out);
+
+/* Number of kernel launches in one forward, and device bytes held. */
+int vla_stats(vla_handle h, int* n_kernels, size_t* device_bytes);
+
+/* Per-stage device time of one forward (ms, CUDA events, outside the graph): vision, prefix, decoder. */
+int vla_time_stages(vla_handle h, float* ms3);
+
+int vla_destroy(vla_handle h);
+const char* vla_last_error(vla_handle h);
+
+/* ---- single operators (used by the kernel-level parity tests and micro-benchmarks) ------------------
+ * All pointers are device pointers; `stream` is a cudaStream_t.  Each call repacks/allocates what it needs
+ * and frees it before returning (synchronous). */
+
+/* Y = epilogue(X[tokens,K] @ W[K,N]) through the tcgen05 kernel.
+ * epi: 0 = bf16 out (+bias, act: 0 none, 1 gelu-tanh, 2 silu, 3 GeGLU with W2), 1 = fp32 residual
+ * (outf = res + bias + gate*acc, in place when res == outf), 2 = QKV+RoPE (N must be 2560; q, kcache, vcache out).
+ * split = cluster size along K (0 = library heuristic), bn = token tile (0 = heuristic). */
+typedef struct vla_gemm_desc {
+  const void* x; int tokens; int K;
+  const void* w; const void* w2; int N;
+  const float* bias; int epi; int act;
+  void* out_bf16; int ld_out;
+  float* out_f32; const float* res; const float* gate; int res_mod;
+  void* q; void* kcache; void* vcache; int pos_off; int rows_per_obs; int kv_obs_stride; int kv_row_off;
+  int split; int bn; int iters; float* ms_per_iter;
+} vla_gemm_desc;
+int vla_op_gemm(const vla_gemm_desc* d, void* stream);
+
+/* O = softmax(mask(Q K^T * scale)) V, bf16.  head_dim 72 or 256.  See attention.cuh for the mask rule. */
+typedef struct vla_attn_desc {
+  const void* q; const void* k; const void* v; void* o;
+  int ldq, ldk, ldv, ldo;
+  int groups_outer, groups_inner;
+  long long q_go, q_gi, k_go, k_gi, v_go, v_gi, o_go, o_gi;
+  int n_q, n_keys, head_dim;
+  int prefix_alloc, valid_prefix, restrict_rows;
+  float scale; int ksplit; int iters; float* ms_per_iter;
+} vla_attn_desc;
+int vla_op_attention(const vla_attn_desc* d, void* stream);
+
+/* y bf16 [rows,D] = norm(x fp32 [rows,D]); mode 0 LayerNorm (w,b), 1 RMS, 2 adaRMS (w = style[3*D]); D 1024|1152|2048. */
+int vla_op_norm(const float* x, void* y, int rows, int D, int mode, const float* w, const float* b, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,133 @@
+"""Shared host logic of Pi0Inference / Pi05Inference: owns one library handle, wraps the library's I/O
+buffers as torch tensors without copying, and mirrors the checkpoint-loading semantics of the reference
+constructors (pi0_infer.py:1337-1338, pi05_infer.py:666-668)."""
+import ctypes as C
+
+import torch
+
+import _capi
+
+
+class _DevMem:
+    """Exposes a raw device allocation to torch through the CUDA array interface (as int16 words)."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes // 2,), "typestr": "<i2", "data": (int(ptr), False),
+                                         "version": 2}
+
+
+def vision_encoder_shapes(nl=27, nle=18):
+    return {
+        "vision_patch_embedding_w": (14, 14, 3, 1152),
+        "vision_patch_embedding_b": (1152,),
+        "vision_position_embedding": (256, 1152),
+        "vision_attn_qkv_w": (nl, 1152, 3 * 1152),
+        "vision_attn_qkv_b": (nl, 3 * 1152),
+        "vision_attn_o_w": (nl, 1152, 1152),
+        "vision_attn_o_b": (nl, 1152),
+        "vision_ffn_up_w": (nl, 1152, 4304),
+        "vision_ffn_up_b": (nl, 4304),
+        "vision_ffn_down_w": (nl, 4304, 1152),
+        "vision_ffn_down_b": (nl, 1152),
+        "vision_pre_attn_norm_w": (nl, 1152),
+        "vision_pre_attn_norm_b": (nl, 1152),
+        "vision_pre_ffn_norm_w": (nl, 1152),
+        "vision_pre_ffn_norm_b": (nl, 1152),
+        "vision_final_norm_w": (1152,),
+        "vision_final_norm_b": (1152,),
+        "encoder_multi_modal_projector_w": (1152, 2048),
+        "encoder_multi_modal_projector_b": (2048,),
+        "encoder_attn_qkv_w": (nle, 2048, 2560),
+        "encoder_attn_o_w": (nle, 2048, 2048),
+        "encoder_ffn_gate_w": (nle, 2048, 16384),
+        "encoder_ffn_up_w": (nle, 2048, 16384),
+        "encoder_ffn_down_w": (nle, 16384, 2048),
+    }
+
+
+class Engine:
+    def __init__(self, model, num_views, chunk_size, prompt_len, shapes, batch=1, device=None,
+                 n_vit_layers=0, n_layers=0, n_steps=0, flags=0):
+        if not torch.cuda.is_available():
+            raise RuntimeError("realtime-vla_b200 needs a CUDA device (B200); there is no CPU path")
+        self.lib = _capi.lib()
+        self.device = torch.device("cuda", torch.cuda.current_device() if device is None else device)
+        cfg = _capi.VlaConfig(model=model, num_views=num_views, chunk_size=chunk_size, prompt_len=prompt_len,
+                              batch=batch, device=self.device.index, n_vit_layers=n_vit_layers,
+                              n_layers=n_layers, n_steps=n_steps, flags=flags)
+        h = C.c_void_p()
+        _capi.check(self.lib.vla_create(C.byref(cfg), C.byref(h)))
+        self.handle = h
+        self.shapes = shapes
+        self.batch = batch
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.vla_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def load(self, key, value):
+        """self.weights[key].copy_(value) of the reference: unknown key -> KeyError, wrong shape -> RuntimeError."""
+        if key not in self.shapes:
+            raise KeyError(key)
+        t = value if isinstance(value, torch.Tensor) else torch.as_tensor(value)
+        want = tuple(self.shapes[key])
+        if tuple(t.shape) != want:
+            raise RuntimeError("checkpoint tensor '%s' has shape %s, expected %s" % (key, tuple(t.shape), want))
+        t = t.detach()
+        if t.dtype == torch.float32:
+            dt = _capi.VLA_F32
+        else:
+            t = t.to(torch.bfloat16)
+            dt = _capi.VLA_BF16
+        t = t.contiguous()
+        shape = (C.c_int64 * max(t.dim(), 1))(*t.shape)
+        _capi.check(self.lib.vla_load_weight(self.handle, key.encode(), C.c_void_p(t.data_ptr()), shape, t.dim(), dt),
+                    self.handle)
+
+    def finalize(self):
+        with torch.cuda.device(self.device):
+            _capi.check(self.lib.vla_finalize(self.handle), self.handle)
+
+    def buffer(self, name, shape, dtype=torch.bfloat16):
+        ptr, nbytes = C.c_void_p(), C.c_size_t()
+        _capi.check(self.lib.vla_buffer(self.handle, name.encode(), C.byref(ptr), C.byref(nbytes)), self.handle)
+        raw = torch.as_tensor(_DevMem(ptr.value, nbytes.value), device=self.device)
+        if dtype == torch.float32:
+            return raw.view(torch.float32).view(shape)
+        return raw.view(dtype).view(shape)
+
+    def set_prompt(self, embeds):
+        embeds = embeds.detach().to(device=self.device, dtype=torch.bfloat16).contiguous()
+        _capi.check(self.lib.vla_set_prompt(self.handle, C.c_void_p(embeds.data_ptr()), embeds.shape[0]), self.handle)
+
+    def forward(self):
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _capi.check(self.lib.vla_forward(self.handle, C.c_void_p(stream)), self.handle)
+
+    def forward_host(self, images, state, noise, out):
+        """Host-memory entry: contiguous bf16 CPU tensors in, actions written to `out` (bf16 CPU)."""
+        _capi.check(self.lib.vla_forward_host(self.handle, C.c_void_p(images.data_ptr()),
+                                              C.c_void_p(state.data_ptr()) if state is not None else None,
+                                              C.c_void_p(noise.data_ptr()), C.c_void_p(out.data_ptr())), self.handle)
+
+    def status_word(self):
+        w = C.c_int()
+        _capi.check(self.lib.vla_status_word(self.handle, C.byref(w)), self.handle)
+        return w.value
+
+    def stats(self):
+        n, b = C.c_int(), C.c_size_t()
+        _capi.check(self.lib.vla_stats(self.handle, C.byref(n), C.byref(b)), self.handle)
+        return n.value, b.value
+
+    def time_stages(self):
+        ms = (C.c_float * 3)()
+        _capi.check(self.lib.vla_time_stages(self.handle, ms), self.handle)
+        return list(ms)

@@ -1,0 +1,142 @@
+// Small memory-bound kernels: row normalisations (fp32 residual stream -> bf16 GEMM operand), patch
+// extraction, weight repacking and casts.
+#pragma once
+#include "common.cuh"
+
+enum NormMode { NORM_LAYER = 0, NORM_RMS = 1, NORM_ADARMS = 2 };
+
+// One CTA (128 threads) per row.  x fp32 [rows, D] -> y bf16 [rows, ld_y].
+//   NORM_LAYER : (x-mean)*rstd*w + b, eps 1e-5        (w, b fp32 [D])
+//   NORM_RMS   : x*rsqrt(mean(x^2)+1e-6)
+//   NORM_ADARMS: x*rsqrt(mean(x^2)+1e-6)*(1+style[d]) + style[D+d]     (style fp32 [3*D])
+template <int D>
+__global__ void __launch_bounds__(128) norm_kernel(const float* __restrict__ x, int ld_x, bf16* __restrict__ y, int ld_y,
+                                                   int mode, const float* __restrict__ w, const float* __restrict__ b,
+                                                   int in_rpo, int in_obs_stride, int in_row_off) {
+  constexpr int PER = (D + 127) / 128;
+  __shared__ float red[2][4];
+  pdl_wait();
+  pdl_trigger();
+  const int row = blockIdx.x;
+  // input row remap: output row r reads input row (r / in_rpo) * in_obs_stride + in_row_off + r % in_rpo
+  const int in_row = in_rpo > 0 ? (row / in_rpo) * in_obs_stride + in_row_off + row % in_rpo : row;
+  const float* xr = x + (size_t)in_row * ld_x;
+  float v[PER];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int d = threadIdx.x + i * 128;
+    v[i] = d < D ? xr[d] : 0.f;
+    s += (mode == NORM_LAYER) ? v[i] : v[i] * v[i];
+  }
+  auto block_sum = [&](float val, int slot) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) val += __shfl_xor_sync(0xffffffffu, val, o);
+    if ((threadIdx.x & 31) == 0) red[slot][threadIdx.x >> 5] = val;
+    __syncthreads();
+    return red[slot][0] + red[slot][1] + red[slot][2] + red[slot][3];
+  };
+  float mean = 0.f, rstd;
+  if (mode == NORM_LAYER) {
+    mean = block_sum(s, 0) * (1.0f / D);
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int d = threadIdx.x + i * 128;
+      const float c = d < D ? v[i] - mean : 0.f;
+      q += c * c;
+    }
+    rstd = rsqrtf(block_sum(q, 1) * (1.0f / D) + 1e-5f);
+  } else {
+    rstd = rsqrtf(block_sum(s, 0) * (1.0f / D) + 1e-6f);
+  }
+  bf16* yr = y + (size_t)row * ld_y;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int d = threadIdx.x + i * 128;
+    if (d >= D) continue;
+    float o;
+    if (mode == NORM_LAYER) o = (v[i] - mean) * rstd * w[d] + b[d];
+    else if (mode == NORM_RMS) o = v[i] * rstd;
+    else o = v[i] * rstd * (1.0f + w[d]) + w[D + d];
+    yr[d] = __float2bfloat16(o);
+  }
+}
+
+// images bf16 (nv,224,224,3) -> patches bf16 [nv*256, 640]: row = view*256 + py*16 + px, column =
+// (iy*14 + ix)*3 + c for the 14x14x3 patch, columns 588..639 zero.
+__global__ void patchify_kernel(const bf16* __restrict__ img, bf16* __restrict__ out, int n_rows) {
+  pdl_wait();
+  pdl_trigger();
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_rows * 640) return;
+  const int row = idx / 640, col = idx - row * 640;
+  bf16 val = __float2bfloat16(0.f);
+  if (col < 588) {
+    const int view = row >> 8, py = (row >> 4) & 15, px = row & 15;
+    const int iy = col / 42, rem = col - iy * 42;   // rem = ix*3 + c
+    val = img[(((size_t)view * 224 + py * 14 + iy) * 224 + px * 14) * 3 + rem];
+  }
+  out[idx] = val;
+}
+
+// W bf16 [K, N] row-major (checkpoint layout) -> Wt bf16 [Np, Kp] row-major, zero padded.
+__global__ void repack_kn_to_nk(const bf16* __restrict__ w, int K, int N, bf16* __restrict__ wt, int Kp, int Np) {
+  __shared__ bf16 tile[32][33];
+  const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int k = k0 + i, n = n0 + threadIdx.x;
+    tile[i][threadIdx.x] = (k < K && n < N) ? w[(size_t)k * N + n] : __float2bfloat16(0.f);
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int n = n0 + i, k = k0 + threadIdx.x;
+    if (n < Np && k < Kp) wt[(size_t)n * Kp + k] = tile[threadIdx.x][i];
+  }
+}
+
+__global__ void bf16_to_f32_kernel(const bf16* __restrict__ in, float* __restrict__ out, size_t n, float scale) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = __bfloat162float(in[i]) * scale;
+}
+__global__ void f32_to_bf16_kernel(const float* __restrict__ in, bf16* __restrict__ out, size_t n) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = __float2bfloat16(in[i]);
+}
+// out[i] = bf16(bf16(in[i]) * scale): a multiply carried out in bf16, as torch does for `w *= s` on a bf16 tensor
+__global__ void scale_bf16_kernel(bf16* __restrict__ w, size_t n, float scale) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) w[i] = __float2bfloat16(__bfloat162float(w[i]) * scale);
+}
+// Start of the action-expert stage: fp32 copy of the bf16 noise, and (Pi0) nothing else.
+__global__ void noise_init_kernel(const bf16* __restrict__ noise, float* __restrict__ noise_f32, int n) {
+  pdl_wait();
+  pdl_trigger();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) noise_f32[i] = __bfloat162float(noise[i]);
+}
+// prompt embeddings bf16 [L,2048] -> fp32 residual stream rows obs*P + row_off + i, for every observation
+__global__ void prompt_rows_kernel(const bf16* __restrict__ emb, float* __restrict__ x, int L, int P, int row_off, int batch) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t per = (size_t)L * 2048;
+  if (idx >= per * batch) return;
+  const int b = (int)(idx / per);
+  const size_t r = idx - (size_t)b * per;
+  x[((size_t)b * P + row_off) * 2048 + r] = __bfloat162float(emb[r]);
+}
+// dst rows (b*dst_stride + dst_off) <- src rows b, fp32, `width` columns
+__global__ void copy_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, int width, int dst_stride_rows,
+                                 int dst_off_rows, int batch) {
+  pdl_wait();
+  pdl_trigger();
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= width * batch) return;
+  const int b = idx / width, c = idx - b * width;
+  dst[((size_t)b * dst_stride_rows + dst_off_rows) * width + c] = src[(size_t)b * width + c];
+}

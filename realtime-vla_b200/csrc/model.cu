@@ -1,0 +1,1091 @@
+// Host side of libvla_b200.so: weight repacking, buffer layout, the launch plan of one Pi0 / Pi05 forward,
+// its capture into one CUDA graph, and the C ABI declared in include/vla_b200.h.
+//
+// Data layout in HBM (one observation; a batch multiplies the token counts):
+//   weights      bf16, K-major [features_pad128, K_pad64] per layer (transposed once from the checkpoint's [K, N])
+//   biases, LayerNorm scale/shift, position embedding, adaRMS styles, RoPE tables   fp32
+//   residual streams vision_x [256*nv,1152], encoder_x [P,2048], decoder_x [S,1024], noise [C,32]   fp32
+//   GEMM operands (normalised activations, attention outputs, MLP hidden)   bf16 row-major
+//   K/V cache    bf16 [layer][observation][P + S][256]; prefix rows first, the S suffix rows rewritten each step
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <functional>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/vla_b200.h"
+#include "attention.cuh"
+#include "elementwise.cuh"
+#include "gemm_sm100.cuh"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+// ---------------------------------------------------------------------------------------------------
+// driver entry point for tensor-map encoding (no link-time dependency on libcuda)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// bf16 [rows, K] row-major with row pitch ld (elements): box = 64 (K) x box_rows, 128-byte swizzle.
+bool make_tmap(CUtensorMap* tm, const void* base, long long K, long long rows, long long ld, int box_rows,
+               std::string* err) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) { *err = "cuTensorMapEncodeTiled entry point not found"; return false; }
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[256];
+    snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed (%d) K=%lld rows=%lld ld=%lld box_rows=%d base=%p", (int)r, K,
+             rows, ld, box_rows, base);
+    *err = buf;
+    return false;
+  }
+  return true;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// generic launch with optional cluster dimension and programmatic dependent launch
+template <typename... KArgs, typename... Args>
+cudaError_t launch_ex(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, int cluster_x, bool pdl,
+                      Args&&... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attrs[2];
+  int n = 0;
+  if (cluster_x > 1) {
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = cluster_x;
+    attrs[n].val.clusterDim.y = 1;
+    attrs[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (pdl) {
+    attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// GEMM launch plan
+struct GemmOp {
+  GemmParams p;
+  int bn;
+  bool dual;
+  dim3 grid;
+};
+
+int pick_bn(int tokens) { return tokens <= 64 ? 64 : (tokens <= 128 ? 128 : 256); }
+
+bool can_split(int bn, bool dual) {
+  if (bn == 64) return dual ? GemmCfg<64, true>::CAN_SPLIT : GemmCfg<64, false>::CAN_SPLIT;
+  if (bn == 128) return dual ? GemmCfg<128, true>::CAN_SPLIT : GemmCfg<128, false>::CAN_SPLIT;
+  return dual ? GemmCfg<256, true>::CAN_SPLIT : GemmCfg<256, false>::CAN_SPLIT;
+}
+
+int pick_split(int units, int k_blocks, int bn, bool dual, int sm_count) {
+  if (!can_split(bn, dual)) return 1;
+  int split = 1;
+  while (split < 8 && units * split * 2 <= sm_count + 12 && split * 2 <= k_blocks) split *= 2;
+  return split;
+}
+
+template <int BN, bool DUAL>
+cudaError_t launch_gemm_t(const GemmOp& op, cudaStream_t st, bool pdl) {
+  static bool attr_set = false;
+  auto kern = gemm_sm100_kernel<BN, DUAL>;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN, DUAL>::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  return launch_ex(kern, op.grid, dim3(192), GemmCfg<BN, DUAL>::SMEM_BYTES, st, op.p.split, pdl, op.p);
+}
+
+cudaError_t launch_gemm(const GemmOp& op, cudaStream_t st, bool pdl) {
+  if (op.bn == 64) return op.dual ? launch_gemm_t<64, true>(op, st, pdl) : launch_gemm_t<64, false>(op, st, pdl);
+  if (op.bn == 128) return op.dual ? launch_gemm_t<128, true>(op, st, pdl) : launch_gemm_t<128, false>(op, st, pdl);
+  return op.dual ? launch_gemm_t<256, true>(op, st, pdl) : launch_gemm_t<256, false>(op, st, pdl);
+}
+
+// w / w2: repacked weights [n_feat_pad, Kp]; x: activations [tokens, K] with pitch ldx.
+bool build_gemm(GemmOp* op, const bf16* w, const bf16* w2, int n_feat, int n_feat_pad, int Kp, const bf16* x, int tokens,
+                int Kx, int ldx, const GemmEpi& epi, int* status, int sm_count, int force_bn, int force_split,
+                std::string* err) {
+  memset(op, 0, sizeof *op);
+  op->dual = w2 != nullptr;
+  op->bn = force_bn > 0 ? force_bn : pick_bn(tokens);
+  if (op->bn != 64 && op->bn != 128 && op->bn != 256) { *err = "token tile must be 64, 128 or 256"; return false; }
+  if (Kp % 64 || n_feat_pad % 128) { *err = "repacked weight must be padded to 128 features x 64 K"; return false; }
+  const int tok_tiles = (tokens + op->bn - 1) / op->bn, feat_tiles = n_feat_pad / 128, kb = Kp / 64;
+  int split = force_split > 0 ? force_split : pick_split(tok_tiles * feat_tiles, kb, op->bn, op->dual, sm_count);
+  if (split > 1 && !can_split(op->bn, op->dual)) { *err = "this tile shape cannot split K"; return false; }
+  if (split > 8 || split > kb || (split & (split - 1))) { *err = "split must be 1, 2, 4 or 8 and <= K/64"; return false; }
+  if (!make_tmap(&op->p.tmA, w, Kp, n_feat_pad, Kp, 128, err)) return false;
+  if (w2 && !make_tmap(&op->p.tmA2, w2, Kp, n_feat_pad, Kp, 128, err)) return false;
+  if (!make_tmap(&op->p.tmB, x, Kx, tokens, ldx, op->bn, err)) return false;
+  op->p.n_feat = n_feat;
+  op->p.n_tok = tokens;
+  op->p.k_blocks = kb;
+  op->p.split = split;
+  op->p.status = status;
+  op->p.epi = epi;
+  op->grid = dim3(split, tok_tiles, feat_tiles);
+  return true;
+}
+
+// ---------------------------------------------------------------------------------------------------
+template <int HD>
+cudaError_t launch_attn_t(const AttnParams& p, int groups, cudaStream_t st, bool pdl) {
+  static bool attr_set = false;
+  auto kern = attention_kernel<HD>;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<HD>::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  dim3 grid(p.ksplit, (p.n_q + 63) / 64, groups);
+  return launch_ex(kern, grid, dim3(128), AttnCfg<HD>::SMEM_BYTES, st, p.ksplit, pdl, p);
+}
+cudaError_t launch_attn(const AttnParams& p, int head_dim, int groups, cudaStream_t st, bool pdl) {
+  return head_dim == 72 ? launch_attn_t<72>(p, groups, st, pdl) : launch_attn_t<256>(p, groups, st, pdl);
+}
+int pick_ksplit(int n_q, int n_keys, int groups, int sm_count) {
+  const int ctas = ((n_q + 63) / 64) * groups, blocks = (n_keys + 63) / 64;
+  int ks = 1;
+  while (ks < 8 && ctas * ks * 2 <= sm_count + 12 && ks * 2 <= blocks) ks *= 2;
+  return ks;
+}
+
+cudaError_t launch_norm(const float* x, int ld_x, bf16* y, int ld_y, int rows, int D, int mode, const float* w,
+                        const float* b, int in_rpo, int in_stride, int in_off, cudaStream_t st, bool pdl) {
+  if (D == 1152) return launch_ex(norm_kernel<1152>, dim3(rows), dim3(128), 0, st, 1, pdl, x, ld_x, y, ld_y, mode, w, b, in_rpo, in_stride, in_off);
+  if (D == 2048) return launch_ex(norm_kernel<2048>, dim3(rows), dim3(128), 0, st, 1, pdl, x, ld_x, y, ld_y, mode, w, b, in_rpo, in_stride, in_off);
+  if (D == 1024) return launch_ex(norm_kernel<1024>, dim3(rows), dim3(128), 0, st, 1, pdl, x, ld_x, y, ld_y, mode, w, b, in_rpo, in_stride, in_off);
+  return cudaErrorInvalidValue;
+}
+
+// ---------------------------------------------------------------------------------------------------
+enum WKind { W_MATRIX, W_VECTOR, W_TIME_EMBEDS, W_PROMPT };
+struct WSpec {
+  WKind kind;
+  bool layered;      // first dim = layer count
+  int which_layers;  // 0 vit, 1 transformer, -1 none
+  int K, N;          // matrix: [K,N]; vector: N
+  int lead;          // non-layered vectors with a leading dim (time biases [10,1024], pos emb [256,1152])
+};
+struct WEntry {
+  WSpec spec;
+  int L, Kp, Np;
+  bf16* w = nullptr;   // [L][Np][Kp]
+  float* v = nullptr;  // [L or lead][N (padded to Np for bias of padded matrices)]
+  bool loaded = false;
+};
+
+int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+}  // namespace
+
+// ===================================================================================================
+struct vla_model {
+  vla_config cfg;
+  std::string err;
+  bool pi05;
+  int nv, C, L, B, P, S, T, nvl, nl, nsteps;
+  int sm_count;
+  bool use_pdl, use_graph;
+  bool finalized = false;
+  int valid_len;       // prefix tokens currently valid (views*256 + prompt rows)
+  std::vector<void*> allocs;
+  size_t bytes = 0;
+  std::map<std::string, WEntry> W;
+  std::map<std::string, std::pair<void*, size_t>> named;
+
+  // I/O and activations
+  bf16 *images, *state, *noise, *state_pad;
+  float* noise_f32;
+  bf16 *patches, *vision_xn, *vision_qkv, *vision_attn, *vision_hidden;
+  float* vision_x;
+  float* encoder_x;
+  bf16 *encoder_xn, *encoder_q, *encoder_attn, *encoder_hidden;
+  bf16 *kcache, *vcache;
+  float *decoder_x, *state_tok;
+  bf16 *decoder_xn, *decoder_q, *decoder_attn, *decoder_hidden, *decoder_act, *decoder_xfin;
+  bf16* lang;
+  float *rope_cos, *rope_sin;
+  float *style_attn, *style_ffn, *style_fin;
+  bf16 *time_tmp, *time_emb;
+  int *d_valid_len, *d_pos_base, *d_status;
+
+  struct Op { int stage; bool is_kernel; std::function<cudaError_t(cudaStream_t)> fn; };
+  std::vector<Op> ops;
+  int n_kernels = 0;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t graph_exec = nullptr;
+  cudaStream_t own_stream = nullptr;
+
+  int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    err = buf;
+    g_last_error = buf;
+    return code;
+  }
+  template <typename T>
+  bool dalloc(T** p, size_t count, const char* name = nullptr) {
+    void* q = nullptr;
+    const size_t nbytes = std::max<size_t>(count * sizeof(T), 256);
+    if (cudaMalloc(&q, nbytes) != cudaSuccess) return false;
+    cudaMemset(q, 0, nbytes);
+    allocs.push_back(q);
+    bytes += nbytes;
+    *p = reinterpret_cast<T*>(q);
+    if (name) named[name] = {q, count * sizeof(T)};
+    return true;
+  }
+};
+
+namespace {
+
+#define CK(call)                                                                                        \
+  do {                                                                                                  \
+    cudaError_t e_ = (call);                                                                            \
+    if (e_ != cudaSuccess) return m->fail(VLA_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(e_)); \
+  } while (0)
+
+void add_spec(vla_model* m, const char* key, WKind kind, int which_layers, int K, int N, int lead = 0) {
+  WEntry e;
+  e.spec = {kind, which_layers >= 0, which_layers, K, N, lead};
+  e.L = which_layers == 0 ? m->nvl : (which_layers == 1 ? m->nl : 1);
+  e.Kp = round_up(K > 0 ? K : 1, 64);
+  e.Np = round_up(N, 128);
+  m->W[key] = e;
+}
+
+void declare_weights(vla_model* m) {
+  // shapes: pi0_infer.py:1245-1287, pi05_infer.py:563-611 of the reference
+  add_spec(m, "vision_patch_embedding_w", W_MATRIX, -1, 588, 1152);
+  add_spec(m, "vision_patch_embedding_b", W_VECTOR, -1, 0, 1152);
+  add_spec(m, "vision_position_embedding", W_VECTOR, -1, 0, 1152, 256);
+  add_spec(m, "vision_attn_qkv_w", W_MATRIX, 0, 1152, 3456);
+  add_spec(m, "vision_attn_qkv_b", W_VECTOR, 0, 0, 3456);
+  add_spec(m, "vision_attn_o_w", W_MATRIX, 0, 1152, 1152);
+  add_spec(m, "vision_attn_o_b", W_VECTOR, 0, 0, 1152);
+  add_spec(m, "vision_ffn_up_w", W_MATRIX, 0, 1152, 4304);
+  add_spec(m, "vision_ffn_up_b", W_VECTOR, 0, 0, 4304);
+  add_spec(m, "vision_ffn_down_w", W_MATRIX, 0, 4304, 1152);
+  add_spec(m, "vision_ffn_down_b", W_VECTOR, 0, 0, 1152);
+  add_spec(m, "vision_pre_attn_norm_w", W_VECTOR, 0, 0, 1152);
+  add_spec(m, "vision_pre_attn_norm_b", W_VECTOR, 0, 0, 1152);
+  add_spec(m, "vision_pre_ffn_norm_w", W_VECTOR, 0, 0, 1152);
+  add_spec(m, "vision_pre_ffn_norm_b", W_VECTOR, 0, 0, 1152);
+  add_spec(m, "vision_final_norm_w", W_VECTOR, -1, 0, 1152);
+  add_spec(m, "vision_final_norm_b", W_VECTOR, -1, 0, 1152);
+  add_spec(m, "encoder_multi_modal_projector_w", W_MATRIX, -1, 1152, 2048);
+  add_spec(m, "encoder_multi_modal_projector_b", W_VECTOR, -1, 0, 2048);
+  add_spec(m, "encoder_attn_qkv_w", W_MATRIX, 1, 2048, 2560);
+  add_spec(m, "encoder_attn_o_w", W_MATRIX, 1, 2048, 2048);
+  add_spec(m, "encoder_ffn_gate_w", W_MATRIX, 1, 2048, 16384);
+  add_spec(m, "encoder_ffn_up_w", W_MATRIX, 1, 2048, 16384);
+  add_spec(m, "encoder_ffn_down_w", W_MATRIX, 1, 16384, 2048);
+  add_spec(m, "decoder_attn_qkv_w", W_MATRIX, 1, 1024, 2560);
+  add_spec(m, "decoder_attn_o_w", W_MATRIX, 1, 2048, 1024);
+  add_spec(m, "decoder_ffn_gate_w", W_MATRIX, 1, 1024, 4096);
+  add_spec(m, "decoder_ffn_up_w", W_MATRIX, 1, 1024, 4096);
+  add_spec(m, "decoder_ffn_down_w", W_MATRIX, 1, 4096, 1024);
+  add_spec(m, "language_embeds", W_PROMPT, -1, 0, 2048);
+  if (!m->pi05) {
+    add_spec(m, "decoder_state_in_proj_w", W_MATRIX, -1, 32, 1024);
+    add_spec(m, "decoder_state_in_proj_b", W_VECTOR, -1, 0, 1024);
+    add_spec(m, "decoder_action_fused_in_proj_w", W_MATRIX, -1, 32, 1024);
+    add_spec(m, "decoder_action_fused_time_biases", W_VECTOR, -1, 0, 1024, 10);
+    add_spec(m, "decoder_action_mlp_w", W_MATRIX, -1, 1024, 1024);
+    add_spec(m, "decoder_action_mlp_b", W_VECTOR, -1, 0, 1024);
+    add_spec(m, "decoder_action_fused_out_proj_w", W_MATRIX, -1, 1024, 32);
+    add_spec(m, "decoder_action_fused_out_proj_b", W_VECTOR, -1, 0, 32);
+  } else {
+    add_spec(m, "decoder_time_embeds", W_TIME_EMBEDS, -1, 0, 1024, 10);
+    add_spec(m, "decoder_time_mlp_in_w", W_MATRIX, -1, 1024, 1024);
+    add_spec(m, "decoder_time_mlp_in_b", W_VECTOR, -1, 0, 1024);
+    add_spec(m, "decoder_time_mlp_out_w", W_MATRIX, -1, 1024, 1024);
+    add_spec(m, "decoder_time_mlp_out_b", W_VECTOR, -1, 0, 1024);
+    add_spec(m, "decoder_action_in_proj_w", W_MATRIX, -1, 32, 1024);
+    add_spec(m, "decoder_action_in_proj_b", W_VECTOR, -1, 0, 1024);
+    add_spec(m, "decoder_pre_attn_norm_mod_w", W_MATRIX, 1, 1024, 3072);
+    add_spec(m, "decoder_pre_attn_norm_mod_b", W_VECTOR, 1, 0, 3072);
+    add_spec(m, "decoder_pre_ffn_norm_mod_w", W_MATRIX, 1, 1024, 3072);
+    add_spec(m, "decoder_pre_ffn_norm_mod_b", W_VECTOR, 1, 0, 3072);
+    add_spec(m, "decoder_action_out_proj_w", W_MATRIX, -1, 1024, 32);
+    add_spec(m, "decoder_action_out_proj_b", W_VECTOR, -1, 0, 32);
+    add_spec(m, "decoder_final_norm_mod_w", W_MATRIX, -1, 1024, 3072);
+    add_spec(m, "decoder_final_norm_mod_b", W_VECTOR, -1, 0, 3072);
+  }
+}
+
+bool alloc_weights(vla_model* m) {
+  for (auto& kv : m->W) {
+    WEntry& e = kv.second;
+    if (e.spec.kind == W_MATRIX) {
+      if (!m->dalloc(&e.w, (size_t)e.L * e.Np * e.Kp)) return false;
+    } else if (e.spec.kind == W_VECTOR) {
+      const int rows = e.spec.layered ? e.L : (e.spec.lead > 0 ? e.spec.lead : 1);
+      if (!m->dalloc(&e.v, (size_t)rows * e.Np)) return false;
+    }
+  }
+  return true;
+}
+
+bool alloc_buffers(vla_model* m) {
+  const size_t B = m->B, Nv = B * m->nv * 256, Np = B * m->P, Ns = B * m->S, Nc = B * m->C;
+  bool ok = true;
+  ok &= m->dalloc(&m->images, Nv * 588, "observation_images_normalized");
+  ok &= m->dalloc(&m->state, B * 32, "observation_state_normalized");
+  ok &= m->dalloc(&m->noise, Nc * 32, "diffusion_noise");
+  ok &= m->dalloc(&m->noise_f32, Nc * 32);
+  ok &= m->dalloc(&m->patches, Nv * 640);
+  ok &= m->dalloc(&m->vision_x, Nv * 1152, "vision_x");
+  ok &= m->dalloc(&m->vision_xn, Nv * 1152);
+  ok &= m->dalloc(&m->vision_qkv, Nv * 3456);
+  ok &= m->dalloc(&m->vision_attn, Nv * 1152);
+  ok &= m->dalloc(&m->vision_hidden, Nv * 4352);
+  ok &= m->dalloc(&m->encoder_x, Np * 2048, "encoder_x");
+  ok &= m->dalloc(&m->encoder_xn, Np * 2048);
+  ok &= m->dalloc(&m->encoder_q, Np * 2048);
+  ok &= m->dalloc(&m->encoder_attn, Np * 2048);
+  ok &= m->dalloc(&m->encoder_hidden, Np * 16384);
+  ok &= m->dalloc(&m->kcache, (size_t)m->nl * B * m->T * 256, "encoder_K");
+  ok &= m->dalloc(&m->vcache, (size_t)m->nl * B * m->T * 256, "encoder_V");
+  ok &= m->dalloc(&m->decoder_x, Ns * 1024, "decoder_x");
+  ok &= m->dalloc(&m->state_tok, B * 1024);
+  ok &= m->dalloc(&m->decoder_xn, Ns * 1024);
+  ok &= m->dalloc(&m->decoder_q, Ns * 2048);
+  ok &= m->dalloc(&m->decoder_attn, Ns * 2048);
+  ok &= m->dalloc(&m->decoder_hidden, Ns * 4096);
+  ok &= m->dalloc(&m->decoder_act, Nc * 1024);
+  ok &= m->dalloc(&m->decoder_xfin, Nc * 1024);
+  ok &= m->dalloc(&m->lang, (size_t)std::max(m->L, 1) * 2048, "language_embeds");
+  ok &= m->dalloc(&m->rope_cos, (size_t)(m->T + 1) * 128);
+  ok &= m->dalloc(&m->rope_sin, (size_t)(m->T + 1) * 128);
+  ok &= m->dalloc(&m->d_valid_len, 1);
+  ok &= m->dalloc(&m->d_pos_base, 1);
+  ok &= m->dalloc(&m->d_status, 1);
+  if (m->pi05) {
+    ok &= m->dalloc(&m->style_attn, (size_t)m->nsteps * m->nl * 3072);
+    ok &= m->dalloc(&m->style_ffn, (size_t)m->nsteps * m->nl * 3072);
+    ok &= m->dalloc(&m->style_fin, (size_t)m->nsteps * 3072);
+    ok &= m->dalloc(&m->time_tmp, (size_t)10 * 1024);
+    ok &= m->dalloc(&m->time_emb, (size_t)10 * 1024);
+  }
+  return ok;
+}
+
+// ---- plan building -------------------------------------------------------------------------------
+struct Plan {
+  vla_model* m;
+  int stage = 0;
+  bool ok = true;
+  std::string err;
+
+  void kernel(std::function<cudaError_t(cudaStream_t)> fn) {
+    m->ops.push_back({stage, true, std::move(fn)});
+    m->n_kernels++;
+  }
+  GemmEpi epi0() { GemmEpi e; memset(&e, 0, sizeof e); return e; }
+
+  // activations x [tokens, Kx] (pitch ldx) times the layer-l slice of weight `key` (+ `key2` for GeGLU)
+  void gemm(const char* key, const char* key2, int layer, const bf16* x, int tokens, int Kx, int ldx, GemmEpi epi,
+            int n_feat_override = 0) {
+    if (!ok) return;
+    WEntry& e = m->W.at(key);
+    const bf16* w = e.w + (size_t)layer * e.Np * e.Kp;
+    const bf16* w2 = key2 ? m->W.at(key2).w + (size_t)layer * e.Np * e.Kp : nullptr;
+    GemmOp op;
+    const int n_feat = n_feat_override > 0 ? n_feat_override : e.spec.N;
+    if (!build_gemm(&op, w, w2, n_feat, e.Np, e.Kp, x, tokens, Kx, ldx, epi, m->d_status, m->sm_count, 0, 0, &err)) {
+      ok = false;
+      err = std::string(key) + ": " + err;
+      return;
+    }
+    const bool pdl = m->use_pdl;
+    kernel([op, pdl](cudaStream_t st) { return launch_gemm(op, st, pdl); });
+  }
+  const float* vec(const char* key, int layer = 0) {
+    WEntry& e = m->W.at(key);
+    return e.v + (size_t)layer * e.Np;
+  }
+  void norm(const float* x, bf16* y, int rows, int D, int mode, const float* w, const float* b, int in_rpo = 0,
+            int in_stride = 0, int in_off = 0) {
+    const bool pdl = m->use_pdl;
+    kernel([=](cudaStream_t st) { return launch_norm(x, D, y, D, rows, D, mode, w, b, in_rpo, in_stride, in_off, st, pdl); });
+  }
+  void attention(AttnParams p, int head_dim, int groups) {
+    const bool pdl = m->use_pdl;
+    p.ksplit = pick_ksplit(p.n_q, p.n_keys, groups, m->sm_count);
+    kernel([=](cudaStream_t st) { return launch_attn(p, head_dim, groups, st, pdl); });
+  }
+};
+
+void plan_vision(Plan& pl) {
+  vla_model* m = pl.m;
+  pl.stage = 0;
+  const bool pdl = m->use_pdl;
+  const int Nv = m->B * m->nv * 256;
+  {
+    const bf16* img = m->images;
+    bf16* out = m->patches;
+    pl.kernel([=](cudaStream_t st) {
+      return launch_ex(patchify_kernel, dim3((Nv * 640 + 255) / 256), dim3(256), 0, st, 1, pdl, img, out, Nv);
+    });
+  }
+  {  // patch embedding + position embedding (pi0_infer.py:348-364)
+    GemmEpi e = pl.epi0();
+    e.kind = EPI_RESID;
+    e.bias = pl.vec("vision_patch_embedding_b");
+    e.outf = m->vision_x; e.ld_outf = 1152;
+    e.res_in = pl.vec("vision_position_embedding"); e.res_mod = 256; e.ld_res = m->W.at("vision_position_embedding").Np;
+    pl.gemm("vision_patch_embedding_w", nullptr, 0, m->patches, Nv, 640, 640, e);
+  }
+  for (int l = 0; l < m->nvl; ++l) {  // pi0_infer.py:607-646
+    pl.norm(m->vision_x, m->vision_xn, Nv, 1152, NORM_LAYER, pl.vec("vision_pre_attn_norm_w", l), pl.vec("vision_pre_attn_norm_b", l));
+    GemmEpi e = pl.epi0();
+    e.kind = EPI_BF16; e.bias = pl.vec("vision_attn_qkv_b", l); e.out = m->vision_qkv; e.ld_out = 3456;
+    pl.gemm("vision_attn_qkv_w", nullptr, l, m->vision_xn, Nv, 1152, 1152, e);
+    AttnParams a; memset(&a, 0, sizeof a);
+    a.q = m->vision_qkv; a.k = m->vision_qkv + 1152; a.v = m->vision_qkv + 2304; a.o = m->vision_attn;
+    a.ldq = a.ldk = a.ldv = 3456; a.ldo = 1152;
+    a.q_go = a.k_go = a.v_go = 256LL * 3456; a.q_gi = a.k_gi = a.v_gi = 72; a.o_go = 256LL * 1152; a.o_gi = 72;
+    a.g_inner = 16; a.n_q = 256; a.n_keys = 256; a.prefix_alloc = 256; a.valid_prefix = 256; a.restrict_rows = 0;
+    a.scale_log2e = 1.4426950408889634f / sqrtf(72.f);
+    pl.attention(a, 72, m->B * m->nv * 16);
+    e = pl.epi0();
+    e.kind = EPI_RESID; e.bias = pl.vec("vision_attn_o_b", l); e.outf = m->vision_x; e.ld_outf = 1152; e.res_in = m->vision_x; e.ld_res = 1152;
+    pl.gemm("vision_attn_o_w", nullptr, l, m->vision_attn, Nv, 1152, 1152, e);
+    pl.norm(m->vision_x, m->vision_xn, Nv, 1152, NORM_LAYER, pl.vec("vision_pre_ffn_norm_w", l), pl.vec("vision_pre_ffn_norm_b", l));
+    e = pl.epi0();
+    e.kind = EPI_BF16; e.act = ACT_GELU; e.bias = pl.vec("vision_ffn_up_b", l); e.out = m->vision_hidden; e.ld_out = 4352;
+    pl.gemm("vision_ffn_up_w", nullptr, l, m->vision_xn, Nv, 1152, 1152, e, 4352);   // pad columns come out as gelu(0)=0
+    e = pl.epi0();
+    e.kind = EPI_RESID; e.bias = pl.vec("vision_ffn_down_b", l); e.outf = m->vision_x; e.ld_outf = 1152; e.res_in = m->vision_x; e.ld_res = 1152;
+    pl.gemm("vision_ffn_down_w", nullptr, l, m->vision_hidden, Nv, 4352, 4352, e);
+  }
+  // final LayerNorm + projector into the prefix residual stream (pi0_infer.py:753-775)
+  pl.norm(m->vision_x, m->vision_xn, Nv, 1152, NORM_LAYER, pl.vec("vision_final_norm_w"), pl.vec("vision_final_norm_b"));
+  GemmEpi e = pl.epi0();
+  e.kind = EPI_RESID; e.bias = pl.vec("encoder_multi_modal_projector_b"); e.outf = m->encoder_x; e.ld_outf = 2048;
+  e.out_rpo = m->nv * 256; e.out_obs_stride = m->P;
+  pl.gemm("encoder_multi_modal_projector_w", nullptr, 0, m->vision_xn, Nv, 1152, 1152, e);
+  if (m->L > 0) {  // pi0_infer.py:1344
+    const bf16* emb = m->lang; float* x = m->encoder_x;
+    const int L = m->L, P = m->P, off = m->nv * 256, B = m->B;
+    pl.kernel([=](cudaStream_t st) {
+      return launch_ex(prompt_rows_kernel, dim3((unsigned)(((size_t)L * 2048 * B + 255) / 256)), dim3(256), 0, st, 1, pdl, emb, x, L, P, off, B);
+    });
+  }
+}
+
+void plan_prefix(Plan& pl) {
+  vla_model* m = pl.m;
+  pl.stage = 1;
+  const int Np = m->B * m->P;
+  for (int l = 0; l < m->nl; ++l) {  // pi0_infer.py:851-884, pi05_infer.py:321-380
+    bf16* kc = m->kcache + (size_t)l * m->B * m->T * 256;
+    bf16* vc = m->vcache + (size_t)l * m->B * m->T * 256;
+    pl.norm(m->encoder_x, m->encoder_xn, Np, 2048, NORM_RMS, nullptr, nullptr);
+    GemmEpi e = pl.epi0();
+    e.kind = EPI_QKV; e.q = m->encoder_q; e.kc = kc; e.vc = vc; e.rope_cos = m->rope_cos; e.rope_sin = m->rope_sin;
+    e.pos_off = 0; e.rows_per_obs = m->P; e.kv_obs_stride = m->T; e.kv_row_off = 0;
+    pl.gemm("encoder_attn_qkv_w", nullptr, l, m->encoder_xn, Np, 2048, 2048, e);
+    if (l == m->nl - 1) break;   // the last prefix layer only feeds the cache
+    AttnParams a; memset(&a, 0, sizeof a);
+    a.q = m->encoder_q; a.k = kc; a.v = vc; a.o = m->encoder_attn;
+    a.ldq = a.ldk = a.ldv = a.ldo = 256;
+    a.q_go = a.o_go = (long long)m->P * 2048; a.k_go = a.v_go = (long long)m->T * 256;
+    a.g_inner = 1; a.n_q = m->P * 8; a.n_keys = m->P; a.prefix_alloc = m->P; a.valid_prefix = m->P;
+    a.valid_prefix_ptr = m->pi05 ? m->d_valid_len : nullptr;
+    a.scale_log2e = 1.4426950408889634f / 16.f;
+    pl.attention(a, 256, m->B);
+    e = pl.epi0();
+    e.kind = EPI_RESID; e.outf = m->encoder_x; e.ld_outf = 2048; e.res_in = m->encoder_x; e.ld_res = 2048;
+    pl.gemm("encoder_attn_o_w", nullptr, l, m->encoder_attn, Np, 2048, 2048, e);
+    pl.norm(m->encoder_x, m->encoder_xn, Np, 2048, NORM_RMS, nullptr, nullptr);
+    e = pl.epi0();
+    e.kind = EPI_BF16; e.act = ACT_GEGLU; e.out = m->encoder_hidden; e.ld_out = 16384;
+    pl.gemm("encoder_ffn_gate_w", "encoder_ffn_up_w", l, m->encoder_xn, Np, 2048, 2048, e);
+    e = pl.epi0();
+    e.kind = EPI_RESID; e.outf = m->encoder_x; e.ld_outf = 2048; e.res_in = m->encoder_x; e.ld_res = 2048;
+    pl.gemm("encoder_ffn_down_w", nullptr, l, m->encoder_hidden, Np, 16384, 16384, e);
+  }
+}
+
+void plan_decoder(Plan& pl) {
+  vla_model* m = pl.m;
+  pl.stage = 2;
+  const bool pdl = m->use_pdl, pi05 = m->pi05;
+  const int Ns = m->B * m->S, Nc = m->B * m->C, B = m->B, S = m->S, C = m->C;
+  {
+    const bf16* nz = m->noise; float* nf = m->noise_f32;
+    pl.kernel([=](cudaStream_t st) {
+      return launch_ex(noise_init_kernel, dim3((Nc * 32 + 255) / 256), dim3(256), 0, st, 1, pdl, nz, nf, Nc * 32);
+    });
+  }
+  if (!pi05) {  // state token, once per forward (pi0_infer.py:1166-1171)
+    GemmEpi e = pl.epi0();
+    e.kind = EPI_RESID; e.bias = pl.vec("decoder_state_in_proj_b"); e.outf = m->state_tok; e.ld_outf = 1024;
+    pl.gemm("decoder_state_in_proj_w", nullptr, 0, m->state, B, 32, 32, e);
+  }
+  for (int step = 0; step < m->nsteps; ++step) {
+    if (!pi05) {  // pi0_infer.py:1173-1185
+      const float* src = m->state_tok; float* dst = m->decoder_x;
+      pl.kernel([=](cudaStream_t st) {
+        return launch_ex(copy_rows_kernel, dim3((1024 * B + 255) / 256), dim3(256), 0, st, 1, pdl, src, dst, 1024, S, 0, B);
+      });
+      GemmEpi e = pl.epi0();
+      e.kind = EPI_BF16; e.act = ACT_SILU; e.bias = pl.vec("decoder_action_fused_time_biases", step % 10);
+      e.out = m->decoder_act; e.ld_out = 1024;
+      pl.gemm("decoder_action_fused_in_proj_w", nullptr, 0, m->noise, Nc, 32, 32, e);
+      e = pl.epi0();
+      e.kind = EPI_RESID; e.bias = pl.vec("decoder_action_mlp_b"); e.outf = m->decoder_x + 1024; e.ld_outf = 1024;
+      e.out_rpo = C; e.out_obs_stride = S;
+      pl.gemm("decoder_action_mlp_w", nullptr, 0, m->decoder_act, Nc, 1024, 1024, e);
+    } else {      // pi05_infer.py:420-425
+      GemmEpi e = pl.epi0();
+      e.kind = EPI_RESID; e.bias = pl.vec("decoder_action_in_proj_b"); e.outf = m->decoder_x; e.ld_outf = 1024;
+      pl.gemm("decoder_action_in_proj_w", nullptr, 0, m->noise, Nc, 32, 32, e);
+    }
+    for (int l = 0; l < m->nl; ++l) {  // pi0_infer.py:1186-1223, pi05_infer.py:427-509
+      bf16* kc = m->kcache + (size_t)l * B * m->T * 256;
+      bf16* vc = m->vcache + (size_t)l * B * m->T * 256;
+      const float* st_attn = pi05 ? m->style_attn + ((size_t)step * m->nl + l) * 3072 : nullptr;
+      const float* st_ffn = pi05 ? m->style_ffn + ((size_t)step * m->nl + l) * 3072 : nullptr;
+      pl.norm(m->decoder_x, m->decoder_xn, Ns, 1024, pi05 ? NORM_ADARMS : NORM_RMS, st_attn, nullptr);
+      GemmEpi e = pl.epi0();
+      e.kind = EPI_QKV; e.q = m->decoder_q; e.kc = kc; e.vc = vc; e.rope_cos = m->rope_cos; e.rope_sin = m->rope_sin;
+      e.pos_off = pi05 ? 0 : m->P; e.pos_base = pi05 ? m->d_pos_base : nullptr;
+      e.rows_per_obs = S; e.kv_obs_stride = m->T; e.kv_row_off = m->P;
+      pl.gemm("decoder_attn_qkv_w", nullptr, l, m->decoder_xn, Ns, 1024, 1024, e);
+      AttnParams a; memset(&a, 0, sizeof a);
+      a.q = m->decoder_q; a.k = kc; a.v = vc; a.o = m->decoder_attn;
+      a.ldq = a.ldk = a.ldv = a.ldo = 256;
+      a.q_go = a.o_go = (long long)S * 2048; a.k_go = a.v_go = (long long)m->T * 256;
+      a.g_inner = 1; a.n_q = S * 8; a.n_keys = m->T; a.prefix_alloc = m->P; a.valid_prefix = m->P;
+      a.valid_prefix_ptr = pi05 ? m->d_valid_len : nullptr;
+      a.restrict_rows = pi05 ? 0 : 8;
+      a.scale_log2e = 1.4426950408889634f / 16.f;
+      pl.attention(a, 256, B);
+      e = pl.epi0();
+      e.kind = EPI_RESID; e.outf = m->decoder_x; e.ld_outf = 1024; e.res_in = m->decoder_x; e.ld_res = 1024;
+      e.gate = pi05 ? st_attn + 2048 : nullptr;
+      pl.gemm("decoder_attn_o_w", nullptr, l, m->decoder_attn, Ns, 2048, 2048, e);
+      pl.norm(m->decoder_x, m->decoder_xn, Ns, 1024, pi05 ? NORM_ADARMS : NORM_RMS, st_ffn, nullptr);
+      e = pl.epi0();
+      e.kind = EPI_BF16; e.act = ACT_GEGLU; e.out = m->decoder_hidden; e.ld_out = 4096;
+      pl.gemm("decoder_ffn_gate_w", "decoder_ffn_up_w", l, m->decoder_xn, Ns, 1024, 1024, e);
+      e = pl.epi0();
+      e.kind = EPI_RESID; e.outf = m->decoder_x; e.ld_outf = 1024; e.res_in = m->decoder_x; e.ld_res = 1024;
+      e.gate = pi05 ? st_ffn + 2048 : nullptr;
+      pl.gemm("decoder_ffn_down_w", nullptr, l, m->decoder_hidden, Ns, 4096, 4096, e);
+    }
+    // Euler update: noise += norm(x_action) @ W_out + b_out   (pi0_infer.py:1224-1230, pi05_infer.py:511-523)
+    if (!pi05) pl.norm(m->decoder_x, m->decoder_xfin, Nc, 1024, NORM_RMS, nullptr, nullptr, C, S, 1);
+    else pl.norm(m->decoder_x, m->decoder_xfin, Nc, 1024, NORM_ADARMS, m->style_fin + (size_t)step * 3072, nullptr);
+    GemmEpi e = pl.epi0();
+    e.kind = EPI_RESID; e.outf = m->noise_f32; e.ld_outf = 32; e.res_in = m->noise_f32; e.ld_res = 32;
+    e.mirror = m->noise; e.ld_mirror = 32;
+    e.bias = pl.vec(pi05 ? "decoder_action_out_proj_b" : "decoder_action_fused_out_proj_b");
+    pl.gemm(pi05 ? "decoder_action_out_proj_w" : "decoder_action_fused_out_proj_w", nullptr, 0, m->decoder_xfin, Nc, 1024, 1024, e);
+  }
+}
+
+int run_ops(vla_model* m, cudaStream_t st, int stage_filter = -1) {
+  for (auto& op : m->ops) {
+    if (stage_filter >= 0 && op.stage != stage_filter) continue;
+    cudaError_t e = op.fn(st);
+    if (e != cudaSuccess) return m->fail(VLA_ERR_CUDA, "launch failed in stage %d: %s", op.stage, cudaGetErrorString(e));
+  }
+  return VLA_OK;
+}
+
+// Pi05 constructor-time work: scaled out-projection, time MLP, adaRMS style rows (pi05_infer.py:669-722)
+int pi05_precompute(vla_model* m, cudaStream_t st) {
+  Plan pl{m};
+  std::vector<vla_model::Op> saved;
+  saved.swap(m->ops);
+  const int saved_n = m->n_kernels;
+  const int ns = m->nsteps;
+  const bf16* te = reinterpret_cast<const bf16*>(m->named["decoder_time_embeds"].first);
+  GemmEpi e = pl.epi0();
+  e.kind = EPI_BF16; e.act = ACT_SILU; e.bias = pl.vec("decoder_time_mlp_in_b"); e.out = m->time_tmp; e.ld_out = 1024;
+  pl.gemm("decoder_time_mlp_in_w", nullptr, 0, te, ns, 1024, 1024, e);
+  e.bias = pl.vec("decoder_time_mlp_out_b"); e.out = m->time_emb;
+  pl.gemm("decoder_time_mlp_out_w", nullptr, 0, m->time_tmp, ns, 1024, 1024, e);
+  for (int l = 0; l < m->nl; ++l) {
+    GemmEpi s = pl.epi0();
+    s.kind = EPI_RESID; s.bias = pl.vec("decoder_pre_attn_norm_mod_b", l); s.outf = m->style_attn + (size_t)l * 3072; s.ld_outf = m->nl * 3072;
+    pl.gemm("decoder_pre_attn_norm_mod_w", nullptr, l, m->time_emb, ns, 1024, 1024, s);
+    s.bias = pl.vec("decoder_pre_ffn_norm_mod_b", l); s.outf = m->style_ffn + (size_t)l * 3072;
+    pl.gemm("decoder_pre_ffn_norm_mod_w", nullptr, l, m->time_emb, ns, 1024, 1024, s);
+  }
+  GemmEpi s = pl.epi0();
+  s.kind = EPI_RESID; s.bias = pl.vec("decoder_final_norm_mod_b"); s.outf = m->style_fin; s.ld_outf = 3072;
+  pl.gemm("decoder_final_norm_mod_w", nullptr, 0, m->time_emb, ns, 1024, 1024, s);
+  int rc = VLA_OK;
+  if (!pl.ok) rc = m->fail(VLA_ERR_CUDA, "pi05 precompute plan: %s", pl.err.c_str());
+  else rc = run_ops(m, st);
+  m->ops.swap(saved);
+  m->n_kernels = saved_n;
+  if (rc) return rc;
+  CK(cudaStreamSynchronize(st));
+  return VLA_OK;
+}
+
+int check_status(vla_model* m) {
+  int w = 0;
+  CK(cudaMemcpy(&w, m->d_status, sizeof w, cudaMemcpyDeviceToHost));
+  if (w) return m->fail(VLA_ERR_DEVICE, "device status word 0x%x (bounded wait timed out or bad shape)", w);
+  return VLA_OK;
+}
+
+}  // namespace
+
+// ===================================================================================================
+extern "C" {
+
+const char* vla_last_error(vla_handle h) { return h ? h->err.c_str() : g_last_error.c_str(); }
+
+int vla_create(const vla_config* cfg, vla_handle* out) {
+  if (!cfg || !out) { g_last_error = "null argument"; return VLA_ERR_STATE; }
+  *out = nullptr;
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+    cudaGetLastError();
+    g_last_error = "no CUDA device: libvla_b200 has no CPU path";
+    return VLA_ERR_CUDA;
+  }
+  vla_model* m = new vla_model();
+  m->cfg = *cfg;
+  auto bail = [&](int code) { g_last_error = m->err; vla_destroy(m); return code; };
+  if (cfg->device < 0 || cfg->device >= ndev) return bail(m->fail(VLA_ERR_SHAPE, "device %d out of range", cfg->device));
+  if (cudaSetDevice(cfg->device) != cudaSuccess) return bail(m->fail(VLA_ERR_CUDA, "cudaSetDevice failed"));
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, cfg->device) != cudaSuccess) return bail(m->fail(VLA_ERR_CUDA, "cudaGetDeviceProperties failed"));
+  if (prop.major != 10) return bail(m->fail(VLA_ERR_CUDA, "device is sm_%d%d; this library is built for sm_100a only", prop.major, prop.minor));
+  m->sm_count = prop.multiProcessorCount;
+  m->pi05 = cfg->model == VLA_PI05;
+  m->nv = cfg->num_views; m->C = cfg->chunk_size; m->L = cfg->prompt_len; m->B = cfg->batch > 0 ? cfg->batch : 1;
+  m->nvl = cfg->n_vit_layers > 0 ? cfg->n_vit_layers : 27;
+  m->nl = cfg->n_layers > 0 ? cfg->n_layers : 18;
+  m->nsteps = cfg->n_steps > 0 ? cfg->n_steps : 10;
+  if (cfg->model != VLA_PI0 && cfg->model != VLA_PI05) return bail(m->fail(VLA_ERR_SHAPE, "unknown model kind %d", cfg->model));
+  if (m->nv < 1 || m->nv > 8 || m->C < 1 || m->L < 0) return bail(m->fail(VLA_ERR_SHAPE, "bad num_views/chunk_size/prompt_len"));
+  if (m->nvl > 27 || m->nl > 18 || m->nsteps > 10) return bail(m->fail(VLA_ERR_SHAPE, "layer/step counts exceed the model's"));
+  m->P = m->nv * 256 + m->L;
+  m->S = m->C + (m->pi05 ? 0 : 1);
+  m->T = m->P + m->S;
+  // the reference's softmax kernels hold one row of <= 1024 keys (pi0_infer.py:1073,1106; pi05_infer.py:295,397)
+  if (m->T > 1024) return bail(m->fail(VLA_ERR_LIMIT, "prefix + suffix = %d keys exceeds the 1024-key limit of the path", m->T));
+  m->valid_len = m->P;
+  m->use_pdl = !(cfg->flags & 1);
+  m->use_graph = !(cfg->flags & 2);
+  declare_weights(m);
+  if (!alloc_weights(m) || !alloc_buffers(m)) return bail(m->fail(VLA_ERR_CUDA, "device allocation failed: %s", cudaGetErrorString(cudaGetLastError())));
+  if (cudaStreamCreateWithFlags(&m->own_stream, cudaStreamNonBlocking) != cudaSuccess) return bail(m->fail(VLA_ERR_CUDA, "stream creation failed"));
+  *out = m;
+  return VLA_OK;
+}
+
+int vla_load_weight(vla_handle m, const char* key, const void* data, const int64_t* shape, int ndim, int dtype) {
+  if (!m || !key || !data || !shape) return VLA_ERR_STATE;
+  cudaSetDevice(m->cfg.device);
+  auto it = m->W.find(key);
+  if (it == m->W.end()) return m->fail(VLA_ERR_KEY, "unknown checkpoint key '%s'", key);
+  WEntry& e = it->second;
+  size_t count = 1;
+  for (int i = 0; i < ndim; ++i) count *= (size_t)shape[i];
+  // expected element count
+  size_t expect;
+  if (e.spec.kind == W_MATRIX) expect = (size_t)e.L * e.spec.K * e.spec.N;
+  else if (e.spec.kind == W_VECTOR) expect = (size_t)(e.spec.layered ? e.L : (e.spec.lead > 0 ? e.spec.lead : 1)) * e.spec.N;
+  else if (e.spec.kind == W_TIME_EMBEDS) expect = (size_t)10 * 1024;
+  else expect = (size_t)m->L * 2048;
+  if (e.spec.kind == W_PROMPT) {
+    if (ndim != 2 || shape[1] != 2048 || shape[0] > m->L)
+      return m->fail(VLA_ERR_SHAPE, "language_embeds must be (<=%d, 2048)", m->L);
+    expect = count;
+  }
+  if (count != expect) return m->fail(VLA_ERR_SHAPE, "'%s': got %zu elements, expected %zu", key, count, expect);
+  if (dtype != VLA_BF16 && dtype != VLA_F32) return m->fail(VLA_ERR_SHAPE, "'%s': dtype must be bf16 or f32", key);
+  if (count == 0) { e.loaded = true; return VLA_OK; }
+
+  // stage the raw tensor on the device as bf16
+  const size_t esz = dtype == VLA_BF16 ? 2 : 4;
+  void* raw = nullptr;
+  CK(cudaMalloc(&raw, count * esz));
+  cudaError_t ce = cudaMemcpy(raw, data, count * esz, cudaMemcpyDefault);
+  bf16* stage = reinterpret_cast<bf16*>(raw);
+  void* conv = nullptr;
+  if (ce == cudaSuccess && dtype == VLA_F32) {
+    ce = cudaMalloc(&conv, count * 2);
+    if (ce == cudaSuccess) {
+      f32_to_bf16_kernel<<<(unsigned)((count + 255) / 256), 256>>>(reinterpret_cast<float*>(raw), reinterpret_cast<bf16*>(conv), count);
+      stage = reinterpret_cast<bf16*>(conv);
+      ce = cudaGetLastError();
+    }
+  }
+  if (ce == cudaSuccess) {
+    if (e.spec.kind == W_MATRIX) {
+      // Pi05 scales the out-projection by -1/steps in place, in bf16, at construction (pi05_infer.py:670-671)
+      if (m->pi05 && !strncmp(key, "decoder_action_out_proj", 23))
+        scale_bf16_kernel<<<(unsigned)((count + 255) / 256), 256>>>(stage, count, -1.0f / 10.0f);
+      for (int l = 0; l < e.L; ++l) {
+        dim3 grid((e.Np + 31) / 32, (e.Kp + 31) / 32), block(32, 8);
+        repack_kn_to_nk<<<grid, block>>>(stage + (size_t)l * e.spec.K * e.spec.N, e.spec.K, e.spec.N,
+                                         e.w + (size_t)l * e.Np * e.Kp, e.Kp, e.Np);
+      }
+    } else if (e.spec.kind == W_VECTOR) {
+      const int rows = e.spec.layered ? e.L : (e.spec.lead > 0 ? e.spec.lead : 1);
+      float scale = 1.0f;
+      if (m->pi05 && !strncmp(key, "decoder_action_out_proj", 23)) {
+        scale_bf16_kernel<<<(unsigned)((count + 255) / 256), 256>>>(stage, count, -1.0f / 10.0f);
+      }
+      for (int r = 0; r < rows; ++r)
+        bf16_to_f32_kernel<<<(e.spec.N + 255) / 256, 256>>>(stage + (size_t)r * e.spec.N, e.v + (size_t)r * e.Np, e.spec.N, scale);
+    } else if (e.spec.kind == W_TIME_EMBEDS) {
+      bf16* dst = nullptr;
+      auto f = m->named.find(key);
+      if (f == m->named.end()) { if (m->dalloc(&dst, count, key)) {} } else dst = reinterpret_cast<bf16*>(f->second.first);
+      if (dst) ce = cudaMemcpy(dst, stage, count * 2, cudaMemcpyDeviceToDevice); else ce = cudaErrorMemoryAllocation;
+    } else {  // prompt
+      ce = cudaMemset(m->lang, 0, (size_t)std::max(m->L, 1) * 2048 * 2);
+      if (ce == cudaSuccess) ce = cudaMemcpy(m->lang, stage, count * 2, cudaMemcpyDeviceToDevice);
+      m->valid_len = m->nv * 256 + (int)shape[0];
+    }
+    if (ce == cudaSuccess) ce = cudaGetLastError();
+    if (ce == cudaSuccess) ce = cudaDeviceSynchronize();
+  }
+  cudaFree(raw);
+  if (conv) cudaFree(conv);
+  if (ce != cudaSuccess) return m->fail(VLA_ERR_CUDA, "'%s': upload/repack failed: %s", key, cudaGetErrorString(ce));
+  e.loaded = true;
+  return VLA_OK;
+}
+
+static int upload_scalars(vla_model* m) {
+  // Pi05: valid prefix length and suffix RoPE start (pi05_infer.py:787-790, 821); Pi0: fixed
+  const int valid = m->valid_len, pos_base = m->valid_len - 1;
+  CK(cudaMemcpy(m->d_valid_len, &valid, sizeof(int), cudaMemcpyHostToDevice));
+  CK(cudaMemcpy(m->d_pos_base, &pos_base, sizeof(int), cudaMemcpyHostToDevice));
+  return VLA_OK;
+}
+
+int vla_set_prompt(vla_handle m, const void* embeds, int len) {
+  if (!m) return VLA_ERR_STATE;
+  cudaSetDevice(m->cfg.device);
+  if (len < 0 || len > m->L) return m->fail(VLA_ERR_SHAPE, "prompt of %d rows does not fit the window of %d", len, m->L);
+  if (!m->pi05 && len != m->L) return m->fail(VLA_ERR_SHAPE, "Pi0 prompt length is fixed at %d", m->L);
+  CK(cudaMemset(m->lang, 0, (size_t)std::max(m->L, 1) * 2048 * 2));
+  if (len > 0) CK(cudaMemcpy(m->lang, embeds, (size_t)len * 2048 * 2, cudaMemcpyDefault));
+  m->valid_len = m->nv * 256 + len;
+  return upload_scalars(m);
+}
+
+int vla_finalize(vla_handle m) {
+  if (!m) return VLA_ERR_STATE;
+  if (m->finalized) return m->fail(VLA_ERR_STATE, "already finalized");
+  cudaSetDevice(m->cfg.device);
+  // RoPE tables, theta 10000, fp32 (pi0_infer.py:1319-1335)
+  {
+    const int n_pos = m->T + 1;
+    std::vector<float> c((size_t)n_pos * 128), s((size_t)n_pos * 128);
+    for (int i = 0; i < 128; ++i) {
+      const float inv_freq = 1.0f / std::pow(10000.0f, (float)(2 * i) / 256.0f);
+      for (int pos = 0; pos < n_pos; ++pos) {
+        const float ph = inv_freq * (float)pos;
+        c[(size_t)pos * 128 + i] = (float)std::cos((double)ph);
+        s[(size_t)pos * 128 + i] = (float)std::sin((double)ph);
+      }
+    }
+    CK(cudaMemcpy(m->rope_cos, c.data(), c.size() * 4, cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(m->rope_sin, s.data(), s.size() * 4, cudaMemcpyHostToDevice));
+  }
+  int rc = upload_scalars(m);
+  if (rc) return rc;
+  if (m->pi05) {
+    if (m->named.find("decoder_time_embeds") == m->named.end()) {
+      bf16* dst = nullptr;
+      if (!m->dalloc(&dst, (size_t)10 * 1024, "decoder_time_embeds")) return m->fail(VLA_ERR_CUDA, "allocation failed");
+    }
+    rc = pi05_precompute(m, m->own_stream);
+    if (rc) return rc;
+  }
+  Plan pl{m};
+  plan_vision(pl);
+  plan_prefix(pl);
+  plan_decoder(pl);
+  if (!pl.ok) return m->fail(VLA_ERR_CUDA, "plan: %s", pl.err.c_str());
+  // one eager run (sets function attributes, surfaces launch errors), then capture (pi0_infer.py:1347-1354)
+  rc = run_ops(m, m->own_stream);
+  if (rc) return rc;
+  CK(cudaStreamSynchronize(m->own_stream));
+  rc = check_status(m);
+  if (rc) return rc;
+  if (m->use_graph) {
+    CK(cudaStreamBeginCapture(m->own_stream, cudaStreamCaptureModeThreadLocal));
+    rc = run_ops(m, m->own_stream);
+    cudaError_t ce = cudaStreamEndCapture(m->own_stream, &m->graph);
+    if (rc) return rc;
+    if (ce != cudaSuccess) return m->fail(VLA_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(ce));
+    CK(cudaGraphInstantiate(&m->graph_exec, m->graph, 0));
+  }
+  m->finalized = true;
+  return VLA_OK;
+}
+
+int vla_buffer(vla_handle m, const char* name, void** dev_ptr, size_t* bytes) {
+  if (!m || !name) return VLA_ERR_STATE;
+  auto it = m->named.find(name);
+  if (it == m->named.end()) return m->fail(VLA_ERR_KEY, "unknown buffer '%s'", name);
+  if (dev_ptr) *dev_ptr = it->second.first;
+  if (bytes) *bytes = it->second.second;
+  return VLA_OK;
+}
+
+int vla_forward(vla_handle m, void* stream) {
+  if (!m || !m->finalized) return m ? m->fail(VLA_ERR_STATE, "forward before finalize") : VLA_ERR_STATE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (m->use_graph) {
+    CK(cudaGraphLaunch(m->graph_exec, st));
+    return VLA_OK;
+  }
+  return run_ops(m, st);
+}
+
+int vla_forward_host(vla_handle m, const void* images, const void* state, const void* noise, void* actions_out) {
+  if (!m || !m->finalized) return m ? m->fail(VLA_ERR_STATE, "forward before finalize") : VLA_ERR_STATE;
+  if (!images || !noise || !actions_out || (!m->pi05 && !state)) return m->fail(VLA_ERR_STATE, "null input");
+  cudaSetDevice(m->cfg.device);
+  cudaStream_t st = m->own_stream;
+  const size_t B = m->B;
+  CK(cudaMemcpyAsync(m->images, images, B * m->nv * 224 * 224 * 3 * 2, cudaMemcpyHostToDevice, st));
+  if (!m->pi05) CK(cudaMemcpyAsync(m->state, state, B * 32 * 2, cudaMemcpyHostToDevice, st));
+  CK(cudaMemcpyAsync(m->noise, noise, B * m->C * 32 * 2, cudaMemcpyHostToDevice, st));
+  int rc = vla_forward(m, st);
+  if (rc) return rc;
+  CK(cudaMemcpyAsync(actions_out, m->noise, B * m->C * 32 * 2, cudaMemcpyDeviceToHost, st));
+  CK(cudaStreamSynchronize(st));
+  return VLA_OK;
+}
+
+int vla_status_word(vla_handle m, int* out) {
+  if (!m || !out) return VLA_ERR_STATE;
+  cudaSetDevice(m->cfg.device);
+  CK(cudaMemcpy(out, m->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  return VLA_OK;
+}
+
+int vla_stats(vla_handle m, int* n_kernels, size_t* device_bytes) {
+  if (!m) return VLA_ERR_STATE;
+  if (n_kernels) *n_kernels = m->n_kernels;
+  if (device_bytes) *device_bytes = m->bytes;
+  return VLA_OK;
+}
+
+int vla_time_stages(vla_handle m, float* ms3) {
+  if (!m || !m->finalized || !ms3) return VLA_ERR_STATE;
+  cudaSetDevice(m->cfg.device);
+  cudaEvent_t ev[4];
+  for (auto& e : ev) CK(cudaEventCreate(&e));
+  cudaStream_t st = m->own_stream;
+  CK(cudaEventRecord(ev[0], st));
+  for (int s = 0; s < 3; ++s) {
+    int rc = run_ops(m, st, s);
+    if (rc) return rc;
+    CK(cudaEventRecord(ev[s + 1], st));
+  }
+  CK(cudaStreamSynchronize(st));
+  for (int s = 0; s < 3; ++s) CK(cudaEventElapsedTime(&ms3[s], ev[s], ev[s + 1]));
+  for (auto& e : ev) cudaEventDestroy(e);
+  return VLA_OK;
+}
+
+int vla_destroy(vla_handle m) {
+  if (!m) return VLA_OK;
+  cudaSetDevice(m->cfg.device);
+  cudaDeviceSynchronize();
+  if (m->graph_exec) cudaGraphExecDestroy(m->graph_exec);
+  if (m->graph) cudaGraphDestroy(m->graph);
+  if (m->own_stream) cudaStreamDestroy(m->own_stream);
+  for (void* p : m->allocs) cudaFree(p);
+  delete m;
+  return VLA_OK;
+}
+
+// ---- single operators ------------------------------------------------------------------------------
+#define CKG(call)                                                                  \
+  do {                                                                             \
+    cudaError_t e_ = (call);                                                       \
+    if (e_ != cudaSuccess) {                                                       \
+      g_last_error = std::string(#call) + " failed: " + cudaGetErrorString(e_);    \
+      rc = VLA_ERR_CUDA;                                                           \
+      goto done;                                                                   \
+    }                                                                              \
+  } while (0)
+
+int vla_op_gemm(const vla_gemm_desc* d, void* stream) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int rc = VLA_OK;
+  bf16 *wt = nullptr, *wt2 = nullptr;
+  float *cosT = nullptr, *sinT = nullptr;
+  int* status = nullptr;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  const int Kp = round_up(d->K, 64), Np = round_up(d->N, 128);
+  int dev = 0, sms = 148;
+  GemmOp op;
+  GemmEpi e;
+  std::string err;
+  memset(&e, 0, sizeof e);
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  CKG(cudaMalloc(&wt, (size_t)Np * Kp * 2));
+  CKG(cudaMalloc(&status, 4));
+  CKG(cudaMemsetAsync(status, 0, 4, st));
+  {
+    dim3 grid((Np + 31) / 32, (Kp + 31) / 32), block(32, 8);
+    repack_kn_to_nk<<<grid, block, 0, st>>>(reinterpret_cast<const bf16*>(d->w), d->K, d->N, wt, Kp, Np);
+    if (d->w2) {
+      CKG(cudaMalloc(&wt2, (size_t)Np * Kp * 2));
+      repack_kn_to_nk<<<grid, block, 0, st>>>(reinterpret_cast<const bf16*>(d->w2), d->K, d->N, wt2, Kp, Np);
+    }
+  }
+  e.kind = d->epi; e.act = d->act; e.bias = d->bias;
+  e.out = reinterpret_cast<bf16*>(d->out_bf16); e.ld_out = d->ld_out > 0 ? d->ld_out : d->N;
+  e.outf = d->out_f32; e.ld_outf = d->N; e.res_in = d->res; e.res_mod = d->res_mod; e.ld_res = d->N; e.gate = d->gate;
+  if (d->epi == EPI_QKV) {
+    if (d->N != 2560) { g_last_error = "QKV epilogue needs N = 2560"; rc = VLA_ERR_SHAPE; goto done; }
+    const int n_pos = d->pos_off + d->rows_per_obs + 1;
+    std::vector<float> c((size_t)n_pos * 128), s((size_t)n_pos * 128);
+    for (int i = 0; i < 128; ++i) {
+      const float inv_freq = 1.0f / std::pow(10000.0f, (float)(2 * i) / 256.0f);
+      for (int pos = 0; pos < n_pos; ++pos) {
+        c[(size_t)pos * 128 + i] = (float)std::cos((double)(inv_freq * (float)pos));
+        s[(size_t)pos * 128 + i] = (float)std::sin((double)(inv_freq * (float)pos));
+      }
+    }
+    CKG(cudaMalloc(&cosT, c.size() * 4));
+    CKG(cudaMalloc(&sinT, s.size() * 4));
+    CKG(cudaMemcpy(cosT, c.data(), c.size() * 4, cudaMemcpyHostToDevice));
+    CKG(cudaMemcpy(sinT, s.data(), s.size() * 4, cudaMemcpyHostToDevice));
+    e.q = reinterpret_cast<bf16*>(d->q); e.kc = reinterpret_cast<bf16*>(d->kcache); e.vc = reinterpret_cast<bf16*>(d->vcache);
+    e.rope_cos = cosT; e.rope_sin = sinT; e.pos_off = d->pos_off; e.rows_per_obs = d->rows_per_obs;
+    e.kv_obs_stride = d->kv_obs_stride; e.kv_row_off = d->kv_row_off;
+  }
+  if (!build_gemm(&op, wt, wt2, d->N, Np, Kp, reinterpret_cast<const bf16*>(d->x), d->tokens, d->K, d->K, e, status, sms,
+                  d->bn, d->split, &err)) {
+    g_last_error = err;
+    rc = VLA_ERR_SHAPE;
+    goto done;
+  }
+  CKG(launch_gemm(op, st, false));
+  CKG(cudaStreamSynchronize(st));
+  if (d->iters > 0 && d->ms_per_iter) {
+    // timing loop: only meaningful for epilogues that are idempotent (not the in-place residual)
+    CKG(cudaEventCreate(&e0));
+    CKG(cudaEventCreate(&e1));
+    CKG(cudaEventRecord(e0, st));
+    for (int i = 0; i < d->iters; ++i) CKG(launch_gemm(op, st, false));
+    CKG(cudaEventRecord(e1, st));
+    CKG(cudaStreamSynchronize(st));
+    float ms = 0.f;
+    CKG(cudaEventElapsedTime(&ms, e0, e1));
+    *d->ms_per_iter = ms / d->iters;
+  }
+  {
+    int w = 0;
+    CKG(cudaMemcpy(&w, status, 4, cudaMemcpyDeviceToHost));
+    if (w) { g_last_error = "device status word raised: bounded wait timed out"; rc = VLA_ERR_DEVICE; }
+  }
+done:
+  if (e0) cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  cudaFree(wt); cudaFree(wt2); cudaFree(cosT); cudaFree(sinT); cudaFree(status);
+  return rc;
+}
+
+int vla_op_attention(const vla_attn_desc* d, void* stream) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int rc = VLA_OK;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (d->head_dim != 72 && d->head_dim != 256) { g_last_error = "head_dim must be 72 or 256"; return VLA_ERR_SHAPE; }
+  AttnParams a;
+  memset(&a, 0, sizeof a);
+  a.q = reinterpret_cast<const bf16*>(d->q); a.k = reinterpret_cast<const bf16*>(d->k);
+  a.v = reinterpret_cast<const bf16*>(d->v); a.o = reinterpret_cast<bf16*>(d->o);
+  a.ldq = d->ldq; a.ldk = d->ldk; a.ldv = d->ldv; a.ldo = d->ldo;
+  a.q_go = d->q_go; a.q_gi = d->q_gi; a.k_go = d->k_go; a.k_gi = d->k_gi; a.v_go = d->v_go; a.v_gi = d->v_gi; a.o_go = d->o_go; a.o_gi = d->o_gi;
+  a.g_inner = d->groups_inner; a.n_q = d->n_q; a.n_keys = d->n_keys;
+  a.prefix_alloc = d->prefix_alloc; a.valid_prefix = d->valid_prefix; a.restrict_rows = d->restrict_rows;
+  a.scale_log2e = d->scale * 1.4426950408889634f;
+  const int groups = d->groups_outer * d->groups_inner;
+  a.ksplit = d->ksplit > 0 ? d->ksplit : pick_ksplit(d->n_q, d->n_keys, groups, sms);
+  if (a.ksplit > 8 || (a.ksplit & (a.ksplit - 1))) { g_last_error = "ksplit must be 1, 2, 4 or 8"; return VLA_ERR_SHAPE; }
+  CKG(launch_attn(a, d->head_dim, groups, st, false));
+  CKG(cudaStreamSynchronize(st));
+  if (d->iters > 0 && d->ms_per_iter) {
+    CKG(cudaEventCreate(&e0));
+    CKG(cudaEventCreate(&e1));
+    CKG(cudaEventRecord(e0, st));
+    for (int i = 0; i < d->iters; ++i) CKG(launch_attn(a, d->head_dim, groups, st, false));
+    CKG(cudaEventRecord(e1, st));
+    CKG(cudaStreamSynchronize(st));
+    float ms = 0.f;
+    CKG(cudaEventElapsedTime(&ms, e0, e1));
+    *d->ms_per_iter = ms / d->iters;
+  }
+done:
+  if (e0) cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  return rc;
+}
+
+int vla_op_norm(const float* x, void* y, int rows, int D, int mode, const float* w, const float* b, void* stream) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  cudaError_t e = launch_norm(x, D, reinterpret_cast<bf16*>(y), D, rows, D, mode, w, b, 0, 0, 0, st, false);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) { g_last_error = std::string("norm failed: ") + cudaGetErrorString(e); return VLA_ERR_CUDA; }
+  return VLA_OK;
+}
+
+}  // extern "C"
