@@ -1,0 +1,348 @@
+"""Benchmark of the Pi0 single-observation forward (the reference's headline: median forward latency,
+benchmark.py:17-33 of the reference; plus observations/s for the data-parallel scaling run).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg1|cfg2|cfg3]
+
+One "step" = one forward of one observation.  The default workload is configuration 2 of BASELINE.json:
+Pi0, 3 views, 20 prompt tokens, chunk 50, 10 Euler steps, full depth, seeded random bf16 weights and inputs
+(no checkpoint or camera data exists offline).  N > 1 runs one independent replica per GPU (the path has no
+cross-observation exchange: weak scaling, no collective on the data path).
+
+Prints one JSON line.  `value` is observations/s over all ranks, timed on the device over exactly K graph
+replays with the inputs resident in HBM; the weights streamed by every forward (5.2 GB) exceed L2 by 40x,
+so no L2 flush is needed between iterations.  `e2e` is the same through the host-memory entry point of the
+C ABI (pinned host buffers in, actions out, copies and synchronisation inside the timed region).
+`--impl reference` times the fp32 CPU oracle (the reference has no CPU path of its own) on the host cores.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "realtime-vla_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    "cfg1": dict(model="pi0", num_views=1, prompt_len=0, chunk=50, seed=0),
+    "cfg2": dict(model="pi0", num_views=3, prompt_len=20, chunk=50, seed=0),
+    "cfg3": dict(model="pi05", num_views=2, prompt_len=52, chunk=50, seed=1),
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from the ncu
+# capture summarised under profiles/), keyed by workload; None until a capture exists.
+NCU_TRAFFIC_BYTES = {"cfg2": None, "cfg1": None, "cfg3": None}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def fast_checkpoint(model, prompt_len, seed, device):
+    """Random bf16 checkpoint of the full-depth shapes, drawn on `device` (timing only: values follow the
+    same N(0, 0.02) / unit-LayerNorm recipe as the parity tests but from the device generator)."""
+    from oracle import synth
+    shapes = {}
+    shapes.update(synth.vision_shapes(27))
+    shapes.update(synth.encoder_shapes(18))
+    shapes.update(synth.pi0_decoder_shapes(18) if model == "pi0" else synth.pi05_decoder_shapes(18))
+    g = torch.Generator(device=device).manual_seed(seed)
+    ck = {}
+    for k, shp in shapes.items():
+        if k.endswith("_norm_w"):
+            ck[k] = torch.ones(shp, dtype=torch.bfloat16, device=device)
+        elif k.endswith("_norm_b"):
+            ck[k] = torch.zeros(shp, dtype=torch.bfloat16, device=device)
+        elif k == "decoder_time_embeds":
+            from oracle.vla_oracle import sincos_time_table
+            ck[k] = sincos_time_table(10).to(device)
+        else:
+            std = 0.002 if k.startswith("decoder_action_fused_out_proj") else 0.02
+            ck[k] = (torch.randn(shp, generator=g, device=device, dtype=torch.float32) * std).to(torch.bfloat16)
+    ck["language_embeds"] = (torch.randn(prompt_len, 2048, generator=g, device=device) * 0.02 * 2048 ** 0.5).to(torch.bfloat16)
+    return ck
+
+
+def inputs(wl, device):
+    g = torch.Generator(device=device).manual_seed(1234)
+    images = (torch.rand(wl["num_views"], 224, 224, 3, generator=g, device=device) * 2 - 1).to(torch.bfloat16)
+    state = torch.randn(32, generator=g, device=device).to(torch.bfloat16)
+    noise = torch.randn(wl["chunk"], 32, generator=g, device=device).to(torch.bfloat16)
+    return images, state, noise
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not self.proc:
+            return out
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, reasons, mx = [], set(), None
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                sm.append(float(f[1]))
+                mx = float(f[2])
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            sm.sort()
+            out = {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+        return out
+
+
+def percentile(xs, q):
+    xs = sorted(xs)
+    return xs[min(len(xs) - 1, int(round(q * (len(xs) - 1))))]
+
+
+def dominant_kernel_roofline(wl, device):
+    """Times the dominant kernel of the workload alone (CUDA events around back-to-back launches on one stream)
+    and returns the roofline object.  For every Pi0/Pi05 configuration that kernel is the prefix GeGLU GEMM:
+    hidden[P,16384] = gelu(x Wg) * (x Wu), 4*P*2048*16384 FLOPs per launch (two P x 2048 x 16384 products), tensor-bound when P >= 512 and
+    co-limited by the 134 MB weight stream at P = 256."""
+    import vla_ops as gpu_ops
+    P = wl["num_views"] * 256 + wl["prompt_len"]
+    g = torch.Generator(device=device).manual_seed(7)
+    x = torch.randn(P, 2048, generator=g, device=device).to(torch.bfloat16)
+    wg = (torch.randn(2048, 16384, generator=g, device=device) * 0.02).to(torch.bfloat16)
+    wu = (torch.randn(2048, 16384, generator=g, device=device) * 0.02).to(torch.bfloat16)
+    _, ms = gpu_ops.gemm(x, wg, w2=wu, act=3, iters=20)
+    flops = 4.0 * P * 2048 * 16384
+    pk, which = peaks()
+    achieved = flops / (ms * 1e-3) / 1e12
+    return {"kernel": "gemm_sm100_kernel<256,dual> prefix GeGLU P=%d" % P, "bound": "tensor", "achieved": round(achieved, 1),
+            "peak": pk["bf16_tflops"], "peak_source": which + " burst", "unit": "TFLOP/s",
+            "frac": round(achieved / pk["bf16_tflops"], 4), "ms_per_launch": round(ms, 4),
+            "traffic": None}
+
+
+def oracle_forward_fn(wl, ck):
+    from oracle import vla_oracle as O
+    w = {k: v.cpu() for k, v in ck.items()}
+    images, state, noise = [t.cpu() for t in inputs(wl, "cpu")]
+    if wl["model"] == "pi0":
+        return lambda: O.pi0_forward(w, images, state, noise)
+    return lambda: O.pi05_forward(w, images, noise)
+
+
+def cpu_baseline(wl, ck, budget_s=25.0):
+    """The fp32 oracle on the host cores: one full forward of the same workload (a bounded sample of 1 step)."""
+    fn = oracle_forward_fn(wl, ck)
+    t0 = time.time()
+    fn()
+    dt = time.time() - t0
+    return {"value": round(1.0 / dt, 5), "unit": "obs/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": "1 full forward of the workload (no warm-up), %.1f s" % dt}
+
+
+def run_reference(args, wl, rank, world):
+    if rank != 0:
+        return
+    device = "cuda" if torch.cuda.is_available() else "cpu"
+    ck = fast_checkpoint(wl["model"], wl["prompt_len"], wl["seed"], device)
+    fn = oracle_forward_fn(wl, ck)
+    del ck
+    warm = min(args.warmup, 1)
+    for _ in range(warm):
+        fn()
+    times, t_start = [], time.time()
+    for _ in range(args.steps):
+        t0 = time.time()
+        fn()
+        times.append(time.time() - t0)
+        if time.time() - t_start > 150:      # keep the whole run within a few minutes
+            break
+    total = sum(times)
+    val = len(times) / total
+    line = {"impl": "reference", "metric": "observations_per_s", "value": round(val, 5), "unit": "obs/s", "n_gpus": args.gpus,
+            "steps": len(times), "warmup": warm, "ms_per_step": round(1e3 * total / len(times), 2), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.workload, **{k: wl[k] for k in ("model", "num_views", "prompt_len", "chunk")},
+                       "euler_steps": 10, "note": "fp32 eager PyTorch oracle on host cores; the reference has no CPU path"},
+            "latency_ms": {"p50": round(1e3 * percentile(times, 0.5), 2), "p99": round(1e3 * percentile(times, 0.99), 2)},
+            "cpu_baseline": {"value": round(val, 5), "unit": "obs/s", "cores": torch.get_num_threads(), "kind": "port",
+                             "sample": "%d full forwards" % len(times)},
+            "e2e": {"value": round(val, 5), "unit": "obs/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-forward", action="store_true",
+                    help="run two forwards and bracket the second with cudaProfilerStart/Stop (for ncu "
+                         "--profile-from-start off); prints no benchmark line")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, wl, rank, world)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a GPU (no CPU fallback for the product path)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=device)
+
+    if wl["model"] == "pi0":
+        from pi0_infer import Pi0Inference
+        ck = fast_checkpoint("pi0", wl["prompt_len"], wl["seed"], device)
+        infer = Pi0Inference(ck, wl["num_views"], wl["chunk"], device=local)
+        images, state, noise = inputs(wl, device)
+        step = lambda: infer.forward(images, state, noise)
+        host_args = [t.cpu().pin_memory() for t in (images, state, noise)]
+        host_step = lambda: infer.forward_host(*host_args)
+    else:
+        from pi05_infer import Pi05Inference
+        ck = fast_checkpoint("pi05", wl["prompt_len"], wl["seed"], device)
+        infer = Pi05Inference(ck, wl["num_views"], wl["chunk"], discrete_state_input=False, device=local)
+        images, state, noise = inputs(wl, device)
+        step = lambda: infer.forward(images, noise)
+        host_args = [t.cpu().pin_memory() for t in (images, noise)]
+        host_step = lambda: infer.forward_host(*host_args)
+    n_kernels, dev_bytes = infer._engine.stats()
+    if args.profile_forward:
+        step()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        step()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print("profiled one forward of %s: %d kernel launches" % (args.workload, n_kernels))
+        return
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    # ---- timed region: exactly K steps, device time -------------------------------------------------
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    total_ms = e0.elapsed_time(e1)
+    # ---- per-step latency (device events around each forward, host sync between) -----------------------
+    lat = []
+    for _ in range(args.steps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        step()
+        b.record()
+        torch.cuda.synchronize()
+        lat.append(a.elapsed_time(b))
+    # ---- end to end through the host-memory entry point ---------------------------------------------------
+    for _ in range(3):
+        host_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        host_step()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop() if rank == 0 else None
+    assert infer._engine.status_word() == 0, "device status word raised"
+
+    t = torch.tensor([total_ms, e2e_s * 1e3], device=device, dtype=torch.float64)
+    if dist:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms = t.tolist()
+    stage_ms = infer._engine.time_stages()
+
+    if rank == 0:
+        h2d = sum(x.numel() * 2 for x in host_args)
+        d2h = wl["chunk"] * 32 * 2
+        line = {"metric": "observations_per_s", "value": round(world * args.steps / (total_ms * 1e-3), 3), "unit": "obs/s",
+                "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": round(total_ms / args.steps, 4),
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": args.workload, **{k: wl[k] for k in ("model", "num_views", "prompt_len", "chunk")},
+                           "euler_steps": 10, "batch_per_gpu": 1, "parallelism": "replicas x%d" % world,
+                           "l2": "5.2 GB of weights streamed per step, 40x the 126 MB L2; no flush needed"},
+                "latency_ms": {"p50": round(percentile(lat, 0.5), 4), "p99": round(percentile(lat, 0.99), 4)},
+                "stage_ms": {"vision": round(stage_ms[0], 4), "prefix": round(stage_ms[1], 4), "decoder": round(stage_ms[2], 4),
+                             "note": "eager launches with events between stages, outside the graph"},
+                "e2e": {"value": round(world * args.steps / (e2e_ms * 1e-3), 3), "unit": "obs/s", "h2d_bytes_per_step": h2d,
+                        "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms / args.steps, 4)},
+                "gpu_launches": n_kernels * args.steps, "kernels_per_step": n_kernels, "device_bytes": dev_bytes,
+                "clocks": clocks}
+        del infer
+        torch.cuda.empty_cache()
+        line["roofline"] = dominant_kernel_roofline(wl, device)
+        line["roofline"]["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload)
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(wl, ck)
+        print(json.dumps(line), flush=True)
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -4,8 +4,9 @@
 //
 // One CTA = 64 query rows (4 warps x 16 rows), streaming 64-key blocks through shared memory, online
 // softmax, bf16 mma.sync (m16n8k16) with fp32 accumulation.  The keys can be split over the CTAs of a
-// cluster (grid.x = cluster size); the partial (max, sum, output) triples are merged through distributed
-// shared memory in fixed order.  No logits or probabilities are written to global memory.
+// cluster (grid.x = cluster size); the partial (max, sum, output) triples are merged in fixed order through
+// a small global scratch that stays in L2 (distributed shared memory was several times slower for this
+// all-to-all pattern).  No logits or probabilities are written to global memory.
 //
 // Visibility of key j for query row i:
 //     j < n_keys  &&  ( j < valid_prefix  ||  ( j >= prefix_alloc && (i >= restrict_rows || j <= prefix_alloc) ) )
@@ -26,6 +27,7 @@ struct AttnParams {
   int restrict_rows;
   float scale_log2e;                      // softmax scale * log2(e)
   int ksplit;                             // cluster size along keys
+  float* scratch;                         // partial outputs of the key splits (ksplit > 1)
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
@@ -61,9 +63,9 @@ struct AttnCfg {
   static constexpr int CHUNKS = HD * 2 / 16;             // 16-byte chunks of real data per row
   static constexpr int TILE_BYTES = 64 * ROW_BYTES;
   static constexpr int KV_BUFS = 2;
-  static constexpr int O_BYTES = 64 * HDP * 4;           // fp32 partial output for the cluster merge
   static constexpr int KV_BYTES = 2 * KV_BUFS * TILE_BYTES;
-  static constexpr int SMEM_BYTES = TILE_BYTES + (KV_BYTES > O_BYTES ? KV_BYTES : O_BYTES) + 64 * 2 * 4 + 16;
+  static constexpr int SMEM_BYTES = TILE_BYTES + KV_BYTES + 16;
+  static constexpr int SCRATCH_ROW_FLOATS = HDP + 4;     // per query row and key split: outputs, max, sum
 };
 
 // Load a 64-row tile (rows row0.. of a [*, ld] matrix, HD real columns) into padded shared memory.
@@ -86,8 +88,6 @@ __global__ void __launch_bounds__(128, 1) attention_kernel(const AttnParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   const uint32_t sQ = smem_u32(smem);
   const uint32_t sKV = sQ + C::TILE_BYTES;
-  float* sO = reinterpret_cast<float*>(smem + C::TILE_BYTES);                 // aliases the K/V buffers
-  float* sML = reinterpret_cast<float*>(smem + C::TILE_BYTES + (C::KV_BYTES > C::O_BYTES ? C::KV_BYTES : C::O_BYTES));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
@@ -244,45 +244,63 @@ __global__ void __launch_bounds__(128, 1) attention_kernel(const AttnParams p) {
     return;
   }
 
-  // ---- merge the key splits through distributed shared memory ----
-  __syncthreads();   // K/V buffers are dead; reuse them for the fp32 partial output
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int lr = warp * 16 + g + h * 8;
-#pragma unroll
-    for (int dt = 0; dt < DT; ++dt) {
-      const int d = dt * 8 + tq * 2;
-      sO[lr * C::HDP + d] = acc[dt][h * 2];
-      sO[lr * C::HDP + d + 1] = acc[dt][h * 2 + 1];
-    }
-    if (tq == 0) { sML[lr * 2] = m_run[h]; sML[lr * 2 + 1] = l_run[h]; }
-  }
-  cluster_sync_all();
+  // ---- merge the key splits: partial (O, max, sum) through a global scratch that stays in L2 ----
+  // layout per cluster: [rank][64 rows][HDP + 4] floats, row = HDP outputs then (max, sum, -, -)
+  constexpr int ROWF = C::HDP + 4;
+  float* cl_scratch = p.scratch + ((size_t)blockIdx.z * gridDim.y + blockIdx.y) * ksplit * 64 * ROWF;
   {
-    // this CTA finishes the head-dim slice [d_begin, d_end) of all 64 rows
-    const int d_begin = (int)(((long long)rank * HD) / ksplit) & ~1;
-    const int d_end = rank == ksplit - 1 ? HD : ((int)(((long long)(rank + 1) * HD) / ksplit) & ~1);
-    const int width = (d_end - d_begin) >> 1;          // bf16 pairs
-    const uint32_t sO_a = smem_u32(sO), sML_a = smem_u32(sML);
+    float* mine = cl_scratch + (size_t)rank * 64 * ROWF;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int lr = warp * 16 + g + h * 8;
+#pragma unroll
+      for (int dt = 0; dt < DT; ++dt)
+        __stcg(reinterpret_cast<float2*>(mine + lr * ROWF + dt * 8 + tq * 2), make_float2(acc[dt][h * 2], acc[dt][h * 2 + 1]));
+      if (tq == 0) __stcg(reinterpret_cast<float2*>(mine + lr * ROWF + C::HDP), make_float2(m_run[h], l_run[h]));
+    }
+  }
+  cluster_sync_all();   // release/acquire at cluster scope: all partials of the cluster are visible
+  {
+    // this CTA finishes the head-dim slice [d_begin, d_end) of all 64 rows, 4 columns per thread and step
+    const int d_begin = (int)(((long long)rank * C::HDP) / ksplit) & ~3;
+    const int d_end = rank == ksplit - 1 ? C::HDP : ((int)(((long long)(rank + 1) * C::HDP) / ksplit) & ~3);
+    const int width = (d_end - d_begin) >> 2;          // float4 groups
     for (int idx = threadIdx.x; idx < 64 * width; idx += 128) {
-      const int lr = idx / width, d = d_begin + (idx - lr * width) * 2;
+      const int lr = idx / width, d = d_begin + (idx - lr * width) * 4;
       const int i = row0 + lr;
       if (i >= p.n_q) continue;
+      float2 ml[8];
+      float4 a[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (r < ksplit) {
+          const float* src = cl_scratch + ((size_t)r * 64 + lr) * ROWF;
+          ml[r] = __ldcg(reinterpret_cast<const float2*>(src + C::HDP));
+          a[r] = __ldcg(reinterpret_cast<const float4*>(src + d));
+        }
+      }
       float m_tot = -1e30f;
-      for (int r = 0; r < ksplit; ++r) m_tot = fmaxf(m_tot, dsmem_ld_f32(dsmem_map(sML_a + lr * 8, r)));
-      float l_tot = 0.f, o0 = 0.f, o1 = 0.f;
-      for (int r = 0; r < ksplit; ++r) {
-        const float mr = dsmem_ld_f32(dsmem_map(sML_a + lr * 8, r));
-        const float lr_ = dsmem_ld_f32(dsmem_map(sML_a + lr * 8 + 4, r));
-        const float w = exp2f(mr - m_tot);
-        l_tot += lr_ * w;
-        const uint32_t ro = dsmem_map(sO_a + (uint32_t)(lr * C::HDP + d) * 4u, r);
-        o0 += dsmem_ld_f32(ro) * w;
-        o1 += dsmem_ld_f32(ro + 4) * w;
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        if (r < ksplit) m_tot = fmaxf(m_tot, ml[r].x);
+      float l_tot = 0.f;
+      float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (r < ksplit) {
+          const float w = exp2f(ml[r].x - m_tot);
+          l_tot += ml[r].y * w;
+          o.x += a[r].x * w; o.y += a[r].y * w; o.z += a[r].z * w; o.w += a[r].w * w;
+        }
       }
       const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-      *reinterpret_cast<uint32_t*>(O + (size_t)i * p.ldo + d) = pack_bf16(o0 * inv, o1 * inv);
+      if (d + 3 < HD) {
+        *reinterpret_cast<uint2*>(O + (size_t)i * p.ldo + d) = make_uint2(pack_bf16(o.x * inv, o.y * inv), pack_bf16(o.z * inv, o.w * inv));
+      } else {
+        const float ov[4] = {o.x * inv, o.y * inv, o.z * inv, o.w * inv};
+        for (int e = 0; e < 4; ++e)
+          if (d + e < HD) O[(size_t)i * p.ldo + d + e] = __float2bfloat16(ov[e]);
+      }
     }
   }
-  cluster_sync_all();
 }

@@ -141,6 +141,12 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 // Address of the same shared-memory location in another CTA of the cluster.
 __device__ __forceinline__ uint32_t dsmem_map(uint32_t local_smem_addr, uint32_t rank) {
   uint32_t r;
@@ -149,8 +155,13 @@ __device__ __forceinline__ uint32_t dsmem_map(uint32_t local_smem_addr, uint32_t
 }
 __device__ __forceinline__ float dsmem_ld_f32(uint32_t addr) {
   float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  // volatile keeps it after the (volatile) cluster barrier; no memory clobber, so several loads can be in flight
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
   return v;
+}
+// Store into another CTA's shared memory; made visible to it by the next cluster barrier (release/acquire).
+__device__ __forceinline__ void dsmem_st_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 __device__ __forceinline__ float4 dsmem_ld_f32x4(uint32_t addr) {
   float4 v;
@@ -171,6 +182,6 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 __device__ __forceinline__ float gelu_tanh_f(float x) {
   // x * sigmoid(2*sqrt(2/pi) * x * (1 + 0.044715 x^2))
   const float u = 1.5957691216057308f * x * (1.0f + 0.044715f * x * x);
-  return x / (1.0f + __expf(-u));
+  return __fdividef(x, 1.0f + __expf(-u));
 }
-__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }

@@ -5,11 +5,14 @@
 //   D         = fp32 accumulator in TMEM: lane = feature, column = token
 //
 // One CTA computes a 128-feature x BN-token tile.  Roles: warp 0 = TMA producer, warp 1 = tcgen05.mma
-// issuer (and TMEM owner), warps 2..5 = epilogue (one TMEM lane quarter each).  The K loop can be split
-// over the CTAs of a thread-block cluster (cluster size = split); partial accumulators are then reduced
-// through distributed shared memory in a fixed order, so results do not depend on scheduling.
-// This is what lets the M=51 action-expert layers and the M=256 prefix layers put every SM on the
-// weight stream.  All waits are bounded (see mbar_wait).
+// issuer (and TMEM owner), warps 2..9 = epilogue (two warps per TMEM lane quarter, alternating 32-column
+// chunks).  The K loop can be split over the CTAs of a thread-block cluster (cluster size = split): every
+// CTA then writes its fp32 partial tile to a scratch area in global memory (it stays in L2; distributed
+// shared memory moves only ~15 B/clk per SM and was 3-4x slower here), one cluster barrier orders the
+// writes, and the CTA that owns a column (column c belongs to rank c % split) adds the `split` partials in
+// rank order, so results do not depend on scheduling.  This is what lets the M=51 action-expert layers
+// and the M=256 prefix layers put every SM on the weight stream.  All mbarrier waits are bounded (see
+// mbar_wait).
 #pragma once
 #include "common.cuh"
 
@@ -49,6 +52,17 @@ struct GemmEpi {
   int kv_row_off;         // first cache row for local row 0
 };
 
+// Optional in-kernel timeline for development builds (-DVLA_TRACE): CTA (0,0,0) records clock64() at the
+// phase boundaries into params.trace[slot].  Compiled out otherwise.
+#ifdef VLA_TRACE
+#define GEMM_TRACE(slot)                                                                             \
+  do {                                                                                               \
+    if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) p.trace[slot] = clock64(); \
+  } while (0)
+#else
+#define GEMM_TRACE(slot) do {} while (0)
+#endif
+
 struct GemmParams {
   CUtensorMap tmA;   // weights [features_padded, Kp], box 64 x 128
   CUtensorMap tmA2;  // second weight (GeGLU "up"), only for DUAL
@@ -58,22 +72,28 @@ struct GemmParams {
   int k_blocks;      // Kp / 64
   int split;         // cluster size along K (1 = no cluster)
   int* status;       // device status word
+  float* scratch;    // split-K partial tiles: [tile][src rank][accumulator][column][128 features] fp32
+  long long* trace;  // development timeline (see GEMM_TRACE), normally null
   GemmEpi epi;
 };
 
-template <int BN, bool DUAL>
+constexpr int GEMM_THREADS = 320;
+
+// SPLITK variants are launched as clusters of `split` CTAs along K.
+template <int BN, bool DUAL, bool SPLITK>
 struct GemmCfg {
   static constexpr int A_BYTES = 128 * 64 * 2;
   static constexpr int B_BYTES = BN * 64 * 2;
   static constexpr int STAGE_BYTES = A_BYTES * (DUAL ? 2 : 1) + B_BYTES;
-  static constexpr int MAX_STAGE_SMEM = 200 * 1024;
-  static constexpr int STAGES_RAW = MAX_STAGE_SMEM / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int RECV_BYTES = 0;
+  static constexpr int PARTIAL_FLOATS = 128 * BN * (DUAL ? 2 : 1);   // scratch floats per CTA
+  static constexpr int MAX_SMEM = 204 * 1024;
+  static constexpr int STAGES_RAW = (MAX_SMEM - RECV_BYTES) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : (STAGES_RAW < 1 ? 1 : STAGES_RAW);
+  static constexpr bool VALID = STAGES_RAW >= 3;
   static constexpr int TMEM_COLS = DUAL ? 2 * BN : BN;
   static constexpr int BAR_BYTES = 256;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
-  static constexpr int PARTIAL_BYTES = 128 * BN * 4 * (DUAL ? 2 : 1);  // split-K partial tile
-  static constexpr bool CAN_SPLIT = PARTIAL_BYTES <= STAGES * STAGE_BYTES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + RECV_BYTES + BAR_BYTES + 1024;
 };
 
 // smem matrix descriptor: K-major tile, rows of 128 B, 128-byte swizzle, 8-row groups 1024 B apart.
@@ -81,63 +101,124 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
   return (uint64_t)((smem_addr & 0x3FFFF) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 
-__device__ __forceinline__ void gemm_epilogue_store(const GemmEpi& e, int n, int t, float v, float v2, bool n_ok,
-                                                    int n_feat) {
+// Per-thread epilogue constants (this thread owns feature n for every token column of the tile).
+struct EpiThread {
+  int n;
+  bool n_ok;
+  float bias, gate;
+  int pos_base;
+};
+
+// Applies the epilogue to NC accumulator columns of one feature: column j is token t0 + j*tstride, the
+// first n_valid columns are real (n_valid is uniform over the warp).  The arithmetic of all columns is
+// written as independent chains, and all global loads of the group are issued before the first store, so
+// they overlap instead of forming a load->store->load chain (outputs may alias the residual input).
+template <int NC>
+__device__ __forceinline__ void gemm_epilogue_cols(const GemmEpi& e, const EpiThread& th, int t0, int tstride, int n_valid,
+                                                   const float* v, const float* v2) {
+  const int n = th.n;
   if (e.kind == EPI_BF16) {
-    if (!n_ok) return;
-    if (e.bias) v += e.bias[n];
-    if (e.act == ACT_GELU) v = gelu_tanh_f(v);
-    else if (e.act == ACT_SILU) v = silu_f(v);
-    else if (e.act == ACT_GEGLU) v = gelu_tanh_f(v) * v2;
-    e.out[(size_t)t * e.ld_out + n] = __float2bfloat16(v);
-  } else if (e.kind == EPI_RESID) {
-    if (!n_ok) return;
-    if (e.gate) v *= e.gate[n];
-    if (e.bias) v += e.bias[n];
-    const size_t orow = e.out_rpo > 0 ? (size_t)(t / e.out_rpo) * e.out_obs_stride + t % e.out_rpo : (size_t)t;
-    if (e.res_in) v += e.res_in[(size_t)(e.res_mod > 0 ? t % e.res_mod : (int)orow) * e.ld_res + n];
-    e.outf[orow * e.ld_outf + n] = v;
-    if (e.mirror) e.mirror[orow * e.ld_mirror + n] = __float2bfloat16(v);
-  } else {  // EPI_QKV
-    const int obs = t / e.rows_per_obs, r = t - obs * e.rows_per_obs;
-    const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
-    if (n < 2304) {
-      const int pos = r + e.pos_off + (e.pos_base ? *e.pos_base : 0);
-      const int i = (n & 255) >> 1;
-      const float c = e.rope_cos[pos * 128 + i], s = e.rope_sin[pos * 128 + i];
-      v = (n & 1) ? (v * c + partner * s) : (v * c - partner * s);
-    }
-    if (!n_ok) return;
-    const bf16 o = __float2bfloat16(v);
-    if (n < 2048) {
-      e.q[(size_t)t * 2048 + n] = o;
+    if (!th.n_ok) return;
+    float x[NC];
+    if (e.act == ACT_GEGLU) {
+#pragma unroll
+      for (int j = 0; j < NC; ++j) x[j] = gelu_tanh_f(v[j] + th.bias) * v2[j];
+    } else if (e.act == ACT_GELU) {
+#pragma unroll
+      for (int j = 0; j < NC; ++j) x[j] = gelu_tanh_f(v[j] + th.bias);
+    } else if (e.act == ACT_SILU) {
+#pragma unroll
+      for (int j = 0; j < NC; ++j) x[j] = silu_f(v[j] + th.bias);
     } else {
-      const size_t row = (size_t)obs * e.kv_obs_stride + e.kv_row_off + r;
-      if (n < 2304) e.kc[row * 256 + (n - 2048)] = o;
-      else e.vc[row * 256 + (n - 2304)] = o;
+#pragma unroll
+      for (int j = 0; j < NC; ++j) x[j] = v[j] + th.bias;
+    }
+    bf16* o = e.out + (size_t)t0 * e.ld_out + n;
+    const size_t step = (size_t)tstride * e.ld_out;
+#pragma unroll
+    for (int j = 0; j < NC; ++j)
+      if (j < n_valid) o[j * step] = __float2bfloat16(x[j]);
+  } else if (e.kind == EPI_RESID) {
+    if (!th.n_ok) return;
+    float r[NC];
+    size_t orow[NC];
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      r[j] = 0.f;
+      const int t = t0 + j * tstride;
+      orow[j] = e.out_rpo > 0 ? (size_t)(t / e.out_rpo) * e.out_obs_stride + t % e.out_rpo : (size_t)t;
+      if (j < n_valid && e.res_in) r[j] = e.res_in[(size_t)(e.res_mod > 0 ? t % e.res_mod : (int)orow[j]) * e.ld_res + n];
+    }
+#pragma unroll
+    for (int j = 0; j < NC; ++j) r[j] += v[j] * th.gate + th.bias;
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      if (j < n_valid) {
+        e.outf[orow[j] * e.ld_outf + n] = r[j];
+        if (e.mirror) e.mirror[orow[j] * e.ld_mirror + n] = __float2bfloat16(r[j]);
+      }
+    }
+  } else {  // EPI_QKV
+    float c[NC], s[NC];
+    const int i = (n & 255) >> 1;
+    const bool rot = n < 2304;
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      c[j] = 1.f;
+      s[j] = 0.f;
+      if (j < n_valid && rot) {
+        const int t = t0 + j * tstride;
+        const int pos = t % e.rows_per_obs + e.pos_off + th.pos_base;
+        c[j] = e.rope_cos[pos * 128 + i];
+        s[j] = e.rope_sin[pos * 128 + i];
+      }
+    }
+    const float sgn = (n & 1) ? 1.f : -1.f;
+    float x[NC];
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      const float partner = __shfl_xor_sync(0xffffffffu, v[j], 1);
+      x[j] = v[j] * c[j] + sgn * partner * s[j];
+    }
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      if (j < n_valid) {
+        const int t = t0 + j * tstride;
+        const bf16 o = __float2bfloat16(x[j]);
+        if (n < 2048) {
+          e.q[(size_t)t * 2048 + n] = o;
+        } else {
+          const int obs = t / e.rows_per_obs, r = t - obs * e.rows_per_obs;
+          const size_t row = (size_t)obs * e.kv_obs_stride + e.kv_row_off + r;
+          if (n < 2304) e.kc[row * 256 + (n - 2048)] = o;
+          else e.vc[row * 256 + (n - 2304)] = o;
+        }
+      }
     }
   }
 }
 
-template <int BN, bool DUAL>
-__global__ void __launch_bounds__(192, 1) gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
-  using C = GemmCfg<BN, DUAL>;
+template <int BN, bool DUAL, bool SPLITK>
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
+  using C = GemmCfg<BN, DUAL, SPLITK>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
   uint8_t* smem = smem_raw + pad;
   const uint32_t smem_base = raw_addr + pad;
 
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
-  const uint32_t full_bar = smem_base + C::STAGES * C::STAGE_BYTES;     // [STAGES]
-  const uint32_t empty_bar = full_bar + 8 * C::STAGES;                  // [STAGES]
-  const uint32_t tmem_full_bar = empty_bar + 8 * C::STAGES;             // [1]
+  constexpr int PIPE_BYTES = C::STAGES * C::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PIPE_BYTES + C::RECV_BYTES);
+  const uint32_t full_bar = smem_base + PIPE_BYTES + C::RECV_BYTES;       // [STAGES]
+  const uint32_t empty_bar = full_bar + 8 * C::STAGES;                    // [STAGES]
+  const uint32_t tmem_full_bar = empty_bar + 8 * C::STAGES;               // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int split = p.split;
-  const int rank = blockIdx.x;  // == cluster rank: cluster dims are (split,1,1) and gridDim.x == split
+  if (threadIdx.x == 0) GEMM_TRACE(0);
+  const int split = SPLITK ? p.split : 1;
+  const int rank = SPLITK ? (int)blockIdx.x : 0;  // == cluster rank: cluster dims are (split,1,1), gridDim.x == split
   const int tok0 = blockIdx.y * BN;
   const int feat0 = blockIdx.z * 128;
   const int kb_begin = (int)(((long long)rank * p.k_blocks) / split);
@@ -163,10 +244,12 @@ __global__ void __launch_bounds__(192, 1) gemm_sm100_kernel(const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) GEMM_TRACE(1);
 
   // Everything above is independent of the previous kernel's output.
   pdl_wait();
   pdl_trigger();
+  if (threadIdx.x == 0) GEMM_TRACE(2);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -183,6 +266,7 @@ __global__ void __launch_bounds__(192, 1) gemm_sm100_kernel(const __grid_constan
         if (DUAL) tma_load_2d(st + C::A_BYTES, &p.tmA2, full_bar + 8 * s, k0, feat0, pol_w);
         tma_load_2d(st + C::A_BYTES * (DUAL ? 2 : 1), &p.tmB, full_bar + 8 * s, k0, tok0, pol_x);
       }
+      GEMM_TRACE(3);
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -196,6 +280,7 @@ __global__ void __launch_bounds__(192, 1) gemm_sm100_kernel(const __grid_constan
         ok = mbar_wait(full_bar + 8 * s, ph, abort_flag);
         if (!ok) break;
         tc_fence_after();
+        if (it == 0) GEMM_TRACE(4);
         const uint32_t st = smem_base + s * C::STAGE_BYTES;
         const uint64_t da = umma_desc_sw128(st);
         const uint64_t da2 = umma_desc_sw128(st + C::A_BYTES);
@@ -209,6 +294,7 @@ __global__ void __launch_bounds__(192, 1) gemm_sm100_kernel(const __grid_constan
         umma_commit(empty_bar + 8 * s);  // frees this smem stage once the MMAs have read it
       }
       if (ok) umma_commit(tmem_full_bar);
+      GEMM_TRACE(5);
     }
     __syncwarp();
   }
@@ -216,74 +302,96 @@ __global__ void __launch_bounds__(192, 1) gemm_sm100_kernel(const __grid_constan
   // ---------------- epilogue ----------------
   const bool is_epi = warp >= 2;
   const int q = warp & 3;                 // TMEM lane quarter this warp may read
+  const int half = (warp - 2) >> 2;       // the two warps of a quarter take alternate column chunks
   const int fl = q * 32 + lane;           // feature lane 0..127
   const int n = feat0 + fl;
   const bool n_ok = n < p.n_feat;
+  EpiThread th;   // per-feature constants, fetched while the main loop runs
+  th.n = n;
+  th.n_ok = n_ok;
+  th.bias = (is_epi && n_ok && p.epi.bias) ? p.epi.bias[n] : 0.f;
+  th.gate = (is_epi && n_ok && p.epi.gate) ? p.epi.gate[n] : 1.f;
+  th.pos_base = (p.epi.kind == EPI_QKV && p.epi.pos_base) ? *p.epi.pos_base : 0;
   bool acc_ok = false;
   if (is_epi) {
     acc_ok = mbar_wait(tmem_full_bar, 0, abort_flag);
     tc_fence_after();
+    if (threadIdx.x == 64) GEMM_TRACE(6);
   }
   const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
-  float* part = reinterpret_cast<float*>(smem);   // [acc][col][128] when split > 1 (reuses the stage buffers)
 
-  if (split == 1) {
+  if (!SPLITK || split == 1) {
     if (is_epi && acc_ok) {
-      for (int c0 = 0; c0 < umma_n; c0 += 32) {
+      for (int c0 = 32 * half; c0 < umma_n; c0 += 64) {
         uint32_t v[32], v2[32];
         tmem_ld32(t_lane + c0, v);
         if (DUAL) tmem_ld32(t_lane + BN + c0, v2);
         tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int t = tok0 + c0 + j;
-          if (t < p.n_tok)
-            gemm_epilogue_store(p.epi, n, t, __uint_as_float(v[j]), DUAL ? __uint_as_float(v2[j]) : 0.f, n_ok,
-                                p.n_feat);
-        }
+        const int n_valid = min(32, p.n_tok - (tok0 + c0));
+        gemm_epilogue_cols<32>(p.epi, th, tok0 + c0, 1, n_valid, reinterpret_cast<const float*>(v),
+                               reinterpret_cast<const float*>(v2));
       }
     }
   } else {
+    constexpr int ACCS = DUAL ? 2 : 1;
+    const int n_cols = min(umma_n, p.n_tok - tok0);
+    // scratch of this cluster: [src rank][accumulator][column][128 features]
+    float* tile_scratch = p.scratch + (size_t)(blockIdx.z * gridDim.y + blockIdx.y) * split * C::PARTIAL_FLOATS;
     if (is_epi && acc_ok) {
-      for (int c0 = 0; c0 < umma_n; c0 += 32) {
+      float* mine = tile_scratch + (size_t)rank * C::PARTIAL_FLOATS;
+      for (int c0 = 32 * half; c0 < umma_n; c0 += 64) {
         uint32_t v[32];
-        tmem_ld32(t_lane + c0, v);
-        tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) part[(c0 + j) * 128 + fl] = __uint_as_float(v[j]);
-        if (DUAL) {
-          tmem_ld32(t_lane + BN + c0, v);
+        for (int a = 0; a < ACCS; ++a) {
+          tmem_ld32(t_lane + a * BN + c0, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) part[(BN + c0 + j) * 128 + fl] = __uint_as_float(v[j]);
+          for (int j = 0; j < 32; ++j)
+            if (c0 + j < n_cols) __stcg(mine + (a * BN + c0 + j) * 128 + fl, __uint_as_float(v[j]));
         }
       }
     }
     __syncwarp();
-    cluster_sync_all();
+    if (threadIdx.x == 64) GEMM_TRACE(7);
+    cluster_sync_all();   // release/acquire at cluster scope: every partial tile of the cluster is visible
+    if (threadIdx.x == 64) GEMM_TRACE(8);
     if (is_epi) {
-      const int n_cols = min(umma_n, p.n_tok - tok0);
-      const uint32_t my_part = smem_base;
-      for (int c = rank; c < n_cols; c += split) {
-        float s1 = 0.f, s2 = 0.f;
-        for (int r = 0; r < split; ++r) {
-          const uint32_t remote = dsmem_map(my_part, (uint32_t)r);
-          s1 += dsmem_ld_f32(remote + (uint32_t)(c * 128 + fl) * 4u);
-          if (DUAL) s2 += dsmem_ld_f32(remote + (uint32_t)((BN + c) * 128 + fl) * 4u);
+      // this CTA owns columns rank, rank+split, ...; the two warps of a quarter alternate groups of 4 of them
+      const int n_owned = n_cols > rank ? (n_cols - rank + split - 1) / split : 0;
+      for (int i0 = 4 * half; i0 < n_owned; i0 += 8) {
+        float s1[4], s2[4];
+#pragma unroll
+        for (int ci = 0; ci < 4; ++ci) {
+          const int c = rank + (i0 + ci) * split;
+          float a[8], b[8];
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            a[r] = 0.f;
+            b[r] = 0.f;
+            if (r < split && i0 + ci < n_owned) {
+              a[r] = __ldcg(tile_scratch + (size_t)r * C::PARTIAL_FLOATS + c * 128 + fl);
+              if (DUAL) b[r] = __ldcg(tile_scratch + (size_t)r * C::PARTIAL_FLOATS + (BN + c) * 128 + fl);
+            }
+          }
+          s1[ci] = ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
+          s2[ci] = ((b[0] + b[1]) + (b[2] + b[3])) + ((b[4] + b[5]) + (b[6] + b[7]));
         }
-        gemm_epilogue_store(p.epi, n, tok0 + c, s1, s2, n_ok, p.n_feat);
+        const int n_valid = min(4, n_owned - i0);
+        gemm_epilogue_cols<4>(p.epi, th, tok0 + rank + i0 * split, split, n_valid, s1, s2);
       }
     }
-    __syncwarp();
-    cluster_sync_all();   // nobody leaves while a peer may still read its partial tile
+    if (threadIdx.x == 64) GEMM_TRACE(9);
   }
 
   // ---------------- teardown ----------------
+  if (threadIdx.x == 64) GEMM_TRACE(11);
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) GEMM_TRACE(12);
   if (*abort_flag) {
     if (threadIdx.x == 0 && p.status) atomicOr(p.status, VLA_ST_WAIT_TIMEOUT);
     for (int i = 0; i < 32; ++i) __nanosleep(1000);   // let any copy still in flight land before the CTA exits
   }
   if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+  if (threadIdx.x == 32) GEMM_TRACE(13);
 }

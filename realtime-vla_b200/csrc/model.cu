@@ -103,37 +103,62 @@ struct GemmOp {
   dim3 grid;
 };
 
-int pick_bn(int tokens) { return tokens <= 64 ? 64 : (tokens <= 128 ? 128 : 256); }
+// Every tile shape exists as a split-K (cluster) variant.
+bool can_split(int, bool) { return true; }
 
-bool can_split(int bn, bool dual) {
-  if (bn == 64) return dual ? GemmCfg<64, true>::CAN_SPLIT : GemmCfg<64, false>::CAN_SPLIT;
-  if (bn == 128) return dual ? GemmCfg<128, true>::CAN_SPLIT : GemmCfg<128, false>::CAN_SPLIT;
-  return dual ? GemmCfg<256, true>::CAN_SPLIT : GemmCfg<256, false>::CAN_SPLIT;
+// Scratch floats a GEMM launch needs for its split-K partial tiles (0 without split).
+size_t gemm_scratch_floats(int bn, bool dual, dim3 grid) {
+  if (grid.x <= 1) return 0;
+  return (size_t)grid.x * grid.y * grid.z * 128 * bn * (dual ? 2 : 1);
 }
 
-int pick_split(int units, int k_blocks, int bn, bool dual, int sm_count) {
-  if (!can_split(bn, dual)) return 1;
+int pick_split(int units, int k_blocks, int sm_count) {
   int split = 1;
-  while (split < 8 && units * split * 2 <= sm_count + 12 && split * 2 <= k_blocks) split *= 2;
+  // clusters of 8 fit about 16 at a time on 148 SMs (8 GPCs), so stay at or below 128 CTAs when splitting
+  while (split < 8 && units * split * 2 <= (sm_count * 7) / 8 && split * 2 <= k_blocks) split *= 2;
   return split;
 }
 
-template <int BN, bool DUAL>
+// Token tile and K split for a GEMM of `tokens` rows over feat_tiles x k_blocks weight tiles: small token
+// counts always fit one tile; for large ones prefer 256-token tiles unless that leaves most SMs idle, in
+// which case 128-token tiles (which can split K) are used.
+void pick_tiling(int tokens, int feat_tiles, int k_blocks, bool dual, int sm_count, int* bn, int* split) {
+  if (tokens <= 64) *bn = 64;
+  else if (tokens <= 128) *bn = 128;
+  else {
+    const int units256 = feat_tiles * ((tokens + 255) / 256);
+    *bn = (dual || units256 * 3 >= sm_count * 2) ? 256 : 128;
+  }
+  const int units = feat_tiles * ((tokens + *bn - 1) / *bn);
+  *split = can_split(*bn, dual) ? pick_split(units, k_blocks, sm_count) : 1;
+}
+
+template <int BN, bool DUAL, bool SPLITK>
 cudaError_t launch_gemm_t(const GemmOp& op, cudaStream_t st, bool pdl) {
+  using C = GemmCfg<BN, DUAL, SPLITK>;
+  static_assert(C::VALID, "tile shape leaves fewer than 3 pipeline stages");
   static bool attr_set = false;
-  auto kern = gemm_sm100_kernel<BN, DUAL>;
+  auto kern = gemm_sm100_kernel<BN, DUAL, SPLITK>;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN, DUAL>::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  return launch_ex(kern, op.grid, dim3(192), GemmCfg<BN, DUAL>::SMEM_BYTES, st, op.p.split, pdl, op.p);
+  return launch_ex(kern, op.grid, dim3(GEMM_THREADS), C::SMEM_BYTES, st, op.p.split, pdl, op.p);
 }
 
 cudaError_t launch_gemm(const GemmOp& op, cudaStream_t st, bool pdl) {
-  if (op.bn == 64) return op.dual ? launch_gemm_t<64, true>(op, st, pdl) : launch_gemm_t<64, false>(op, st, pdl);
-  if (op.bn == 128) return op.dual ? launch_gemm_t<128, true>(op, st, pdl) : launch_gemm_t<128, false>(op, st, pdl);
-  return op.dual ? launch_gemm_t<256, true>(op, st, pdl) : launch_gemm_t<256, false>(op, st, pdl);
+  const bool sk = op.p.split > 1;
+  if (op.bn == 64) {
+    if (op.dual) return sk ? launch_gemm_t<64, true, true>(op, st, pdl) : launch_gemm_t<64, true, false>(op, st, pdl);
+    return sk ? launch_gemm_t<64, false, true>(op, st, pdl) : launch_gemm_t<64, false, false>(op, st, pdl);
+  }
+  if (op.bn == 128) {
+    if (op.dual) return sk ? launch_gemm_t<128, true, true>(op, st, pdl) : launch_gemm_t<128, true, false>(op, st, pdl);
+    return sk ? launch_gemm_t<128, false, true>(op, st, pdl) : launch_gemm_t<128, false, false>(op, st, pdl);
+  }
+  if (op.dual) return sk ? launch_gemm_t<256, true, true>(op, st, pdl) : launch_gemm_t<256, true, false>(op, st, pdl);
+  return sk ? launch_gemm_t<256, false, true>(op, st, pdl) : launch_gemm_t<256, false, false>(op, st, pdl);
 }
 
 // w / w2: repacked weights [n_feat_pad, Kp]; x: activations [tokens, K] with pitch ldx.
@@ -142,12 +167,19 @@ bool build_gemm(GemmOp* op, const bf16* w, const bf16* w2, int n_feat, int n_fea
                 std::string* err) {
   memset(op, 0, sizeof *op);
   op->dual = w2 != nullptr;
-  op->bn = force_bn > 0 ? force_bn : pick_bn(tokens);
-  if (op->bn != 64 && op->bn != 128 && op->bn != 256) { *err = "token tile must be 64, 128 or 256"; return false; }
   if (Kp % 64 || n_feat_pad % 128) { *err = "repacked weight must be padded to 128 features x 64 K"; return false; }
-  const int tok_tiles = (tokens + op->bn - 1) / op->bn, feat_tiles = n_feat_pad / 128, kb = Kp / 64;
-  int split = force_split > 0 ? force_split : pick_split(tok_tiles * feat_tiles, kb, op->bn, op->dual, sm_count);
-  if (split > 1 && !can_split(op->bn, op->dual)) { *err = "this tile shape cannot split K"; return false; }
+  const int feat_tiles = n_feat_pad / 128, kb = Kp / 64;
+  int bn, split;
+  pick_tiling(tokens, feat_tiles, kb, op->dual, sm_count, &bn, &split);
+  if (force_bn > 0) {
+    bn = force_bn;
+    if (bn != 64 && bn != 128 && bn != 256) { *err = "token tile must be 64, 128 or 256"; return false; }
+    split = can_split(bn, op->dual) ? pick_split(feat_tiles * ((tokens + bn - 1) / bn), kb, sm_count) : 1;
+  }
+  if (force_split > 0) split = force_split;
+  op->bn = bn;
+  const int tok_tiles = (tokens + bn - 1) / bn;
+  if (split > 1 && !can_split(bn, op->dual)) { *err = "this tile shape has no split-K variant"; return false; }
   if (split > 8 || split > kb || (split & (split - 1))) { *err = "split must be 1, 2, 4 or 8 and <= K/64"; return false; }
   if (!make_tmap(&op->p.tmA, w, Kp, n_feat_pad, Kp, 128, err)) return false;
   if (w2 && !make_tmap(&op->p.tmA2, w2, Kp, n_feat_pad, Kp, 128, err)) return false;
@@ -178,10 +210,15 @@ cudaError_t launch_attn_t(const AttnParams& p, int groups, cudaStream_t st, bool
 cudaError_t launch_attn(const AttnParams& p, int head_dim, int groups, cudaStream_t st, bool pdl) {
   return head_dim == 72 ? launch_attn_t<72>(p, groups, st, pdl) : launch_attn_t<256>(p, groups, st, pdl);
 }
+size_t attn_scratch_floats(const AttnParams& p, int head_dim, int groups) {
+  if (p.ksplit <= 1) return 0;
+  const int hdp = (head_dim + 15) / 16 * 16;
+  return (size_t)groups * ((p.n_q + 63) / 64) * p.ksplit * 64 * (hdp + 4);
+}
 int pick_ksplit(int n_q, int n_keys, int groups, int sm_count) {
   const int ctas = ((n_q + 63) / 64) * groups, blocks = (n_keys + 63) / 64;
   int ks = 1;
-  while (ks < 8 && ctas * ks * 2 <= sm_count + 12 && ks * 2 <= blocks) ks *= 2;
+  while (ks < 8 && ctas * ks * 2 <= (sm_count * 7) / 8 && ks * 2 <= blocks) ks *= 2;
   return ks;
 }
 
@@ -244,6 +281,10 @@ struct vla_model {
   float *style_attn, *style_ffn, *style_fin;
   bf16 *time_tmp, *time_emb;
   int *d_valid_len, *d_pos_base, *d_status;
+  float* gemm_scratch;            // split-K partial tiles of whichever GEMM is running (kernels never overlap)
+  size_t gemm_scratch_cap = 0;    // floats
+  float* attn_scratch;            // key-split partial outputs of whichever attention kernel is running
+  size_t attn_scratch_cap = 0;
 
   struct Op { int stage; bool is_kernel; std::function<cudaError_t(cudaStream_t)> fn; };
   std::vector<Op> ops;
@@ -400,6 +441,10 @@ bool alloc_buffers(vla_model* m) {
   ok &= m->dalloc(&m->d_valid_len, 1);
   ok &= m->dalloc(&m->d_pos_base, 1);
   ok &= m->dalloc(&m->d_status, 1);
+  m->gemm_scratch_cap = (size_t)16 << 20;   // 64 MB: 176 CTAs x the largest partial tile (128 x 256 x 2 fp32)
+  ok &= m->dalloc(&m->gemm_scratch, m->gemm_scratch_cap);
+  m->attn_scratch_cap = (size_t)6 << 20;    // 24 MB: 176 CTAs x 64 rows x 260 fp32, with headroom
+  ok &= m->dalloc(&m->attn_scratch, m->attn_scratch_cap);
   if (m->pi05) {
     ok &= m->dalloc(&m->style_attn, (size_t)m->nsteps * m->nl * 3072);
     ok &= m->dalloc(&m->style_ffn, (size_t)m->nsteps * m->nl * 3072);
@@ -437,6 +482,12 @@ struct Plan {
       err = std::string(key) + ": " + err;
       return;
     }
+    if (gemm_scratch_floats(op.bn, op.dual, op.grid) > m->gemm_scratch_cap) {
+      ok = false;
+      err = std::string(key) + ": split-K scratch too small";
+      return;
+    }
+    op.p.scratch = m->gemm_scratch;
     const bool pdl = m->use_pdl;
     kernel([op, pdl](cudaStream_t st) { return launch_gemm(op, st, pdl); });
   }
@@ -452,6 +503,12 @@ struct Plan {
   void attention(AttnParams p, int head_dim, int groups) {
     const bool pdl = m->use_pdl;
     p.ksplit = pick_ksplit(p.n_q, p.n_keys, groups, m->sm_count);
+    p.scratch = m->attn_scratch;
+    if (attn_scratch_floats(p, head_dim, groups) > m->attn_scratch_cap) {
+      ok = false;
+      err = "attention key-split scratch too small";
+      return;
+    }
     kernel([=](cudaStream_t st) { return launch_attn(p, head_dim, groups, st, pdl); });
   }
 };
@@ -725,7 +782,8 @@ int vla_create(const vla_config* cfg, vla_handle* out) {
 }
 
 int vla_load_weight(vla_handle m, const char* key, const void* data, const int64_t* shape, int ndim, int dtype) {
-  if (!m || !key || !data || !shape) return VLA_ERR_STATE;
+  if (!m) return VLA_ERR_STATE;
+  if (!key || !shape) return m->fail(VLA_ERR_STATE, "null key or shape");
   cudaSetDevice(m->cfg.device);
   auto it = m->W.find(key);
   if (it == m->W.end()) return m->fail(VLA_ERR_KEY, "unknown checkpoint key '%s'", key);
@@ -746,6 +804,7 @@ int vla_load_weight(vla_handle m, const char* key, const void* data, const int64
   if (count != expect) return m->fail(VLA_ERR_SHAPE, "'%s': got %zu elements, expected %zu", key, count, expect);
   if (dtype != VLA_BF16 && dtype != VLA_F32) return m->fail(VLA_ERR_SHAPE, "'%s': dtype must be bf16 or f32", key);
   if (count == 0) { e.loaded = true; return VLA_OK; }
+  if (!data) return m->fail(VLA_ERR_STATE, "'%s': null data pointer", key);
 
   // stage the raw tensor on the device as bf16
   const size_t esz = dtype == VLA_BF16 ? 2 : 4;
@@ -965,7 +1024,7 @@ int vla_op_gemm(const vla_gemm_desc* d, void* stream) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int rc = VLA_OK;
   bf16 *wt = nullptr, *wt2 = nullptr;
-  float *cosT = nullptr, *sinT = nullptr;
+  float *cosT = nullptr, *sinT = nullptr, *scratch = nullptr;
   int* status = nullptr;
   cudaEvent_t e0 = nullptr, e1 = nullptr;
   const int Kp = round_up(d->K, 64), Np = round_up(d->N, 128);
@@ -1015,6 +1074,28 @@ int vla_op_gemm(const vla_gemm_desc* d, void* stream) {
     rc = VLA_ERR_SHAPE;
     goto done;
   }
+  if (gemm_scratch_floats(op.bn, op.dual, op.grid) > 0) {
+    CKG(cudaMalloc(&scratch, gemm_scratch_floats(op.bn, op.dual, op.grid) * sizeof(float)));
+    op.p.scratch = scratch;
+  }
+#ifdef VLA_TRACE
+  {
+    long long* tr = nullptr;
+    CKG(cudaMalloc(&tr, 16 * sizeof(long long)));
+    CKG(cudaMemset(tr, 0, 16 * sizeof(long long)));
+    for (int rep = 0; rep < 3; ++rep) CKG(launch_gemm(op, st, false));   // warm: descriptors, code, L2
+    op.p.trace = tr;
+    CKG(launch_gemm(op, st, false));
+    op.p.trace = nullptr;
+    CKG(cudaStreamSynchronize(st));
+    long long h[16];
+    CKG(cudaMemcpy(h, tr, sizeof h, cudaMemcpyDeviceToHost));
+    cudaFree(tr);
+    printf("trace tokens=%d K=%d N=%d grid=(%d,%d,%d):", d->tokens, d->K, d->N, op.grid.x, op.grid.y, op.grid.z);
+    for (int i = 1; i < 14; ++i) printf(" t%d=%lld", i, h[i] ? h[i] - h[0] : -1);
+    printf("\n");
+  }
+#endif
   CKG(launch_gemm(op, st, false));
   CKG(cudaStreamSynchronize(st));
   if (d->iters > 0 && d->ms_per_iter) {
@@ -1037,7 +1118,7 @@ int vla_op_gemm(const vla_gemm_desc* d, void* stream) {
 done:
   if (e0) cudaEventDestroy(e0);
   if (e1) cudaEventDestroy(e1);
-  cudaFree(wt); cudaFree(wt2); cudaFree(cosT); cudaFree(sinT); cudaFree(status);
+  cudaFree(wt); cudaFree(wt2); cudaFree(cosT); cudaFree(sinT); cudaFree(status); cudaFree(scratch);
   return rc;
 }
 
@@ -1045,6 +1126,7 @@ int vla_op_attention(const vla_attn_desc* d, void* stream) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int rc = VLA_OK;
   cudaEvent_t e0 = nullptr, e1 = nullptr;
+  float* scratch = nullptr;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -1061,6 +1143,10 @@ int vla_op_attention(const vla_attn_desc* d, void* stream) {
   const int groups = d->groups_outer * d->groups_inner;
   a.ksplit = d->ksplit > 0 ? d->ksplit : pick_ksplit(d->n_q, d->n_keys, groups, sms);
   if (a.ksplit > 8 || (a.ksplit & (a.ksplit - 1))) { g_last_error = "ksplit must be 1, 2, 4 or 8"; return VLA_ERR_SHAPE; }
+  if (a.ksplit > 1) {
+    CKG(cudaMalloc(&scratch, attn_scratch_floats(a, d->head_dim, groups) * sizeof(float)));
+    a.scratch = scratch;
+  }
   CKG(launch_attn(a, d->head_dim, groups, st, false));
   CKG(cudaStreamSynchronize(st));
   if (d->iters > 0 && d->ms_per_iter) {
@@ -1077,6 +1163,7 @@ int vla_op_attention(const vla_attn_desc* d, void* stream) {
 done:
   if (e0) cudaEventDestroy(e0);
   if (e1) cudaEventDestroy(e1);
+  cudaFree(scratch);
   return rc;
 }
 

@@ -1,4 +1,5 @@
-"""Thin Python callers of the single-operator C-ABI entry points (vla_op_*), used by the GPU parity tests."""
+"""Python callers of the single-operator C-ABI entry points (vla_op_*): kernel-level parity tests and
+micro-benchmarks call the kernels through these."""
 import ctypes as C
 
 import torch
