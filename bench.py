@@ -158,6 +158,19 @@ def dominant_kernel_roofline(wl, device):
             "traffic": None}
 
 
+def decoder_stream(wl, decoder_ms):
+    """Action-expert weight streaming: algorithmic bytes of the 10 Euler steps (18 layers x 34.603 MB of weights
+    + 2.23 MB of in/out projections + the K/V cache rows read by the suffix attention, per step) over the
+    measured decoder stage time, against the HBM copy peak."""
+    P = wl["num_views"] * 256 + wl["prompt_len"]
+    S = wl["chunk"] + (1 if wl["model"] == "pi0" else 0)
+    per_step = 18 * (34.603e6 + 1024.0 * (P + S)) + 2.23e6
+    gbs = 10 * per_step / (decoder_ms * 1e-3) / 1e9
+    pk, which = peaks()
+    return {"bytes_per_forward": int(10 * per_step), "achieved": round(gbs, 1), "peak": pk["hbm_gbs"], "peak_source": which,
+            "unit": "GB/s", "frac": round(gbs / pk["hbm_gbs"], 4), "bound": "hbm"}
+
+
 def oracle_forward_fn(wl, ck):
     from oracle import vla_oracle as O
     w = {k: v.cpu() for k, v in ck.items()}
@@ -217,6 +230,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--microbench", action="store_true",
+                    help="time only the dominant kernel of the workload (prefix GeGLU GEMM) and print its roofline object")
     ap.add_argument("--profile-forward", action="store_true",
                     help="run two forwards and bracket the second with cudaProfilerStart/Stop (for ncu "
                          "--profile-from-start off); prints no benchmark line")
@@ -234,6 +249,9 @@ def main():
         raise SystemExit("bench.py needs a GPU (no CPU fallback for the product path)")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    if args.microbench:
+        print(json.dumps(dominant_kernel_roofline(wl, device)), flush=True)
+        return
     dist = None
     if world > 1:
         import torch.distributed as dist_mod
@@ -330,6 +348,7 @@ def main():
                              "note": "eager launches with events between stages, outside the graph"},
                 "e2e": {"value": round(world * args.steps / (e2e_ms * 1e-3), 3), "unit": "obs/s", "h2d_bytes_per_step": h2d,
                         "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms / args.steps, 4)},
+                "decoder_stream": decoder_stream(wl, stage_ms[2]),
                 "gpu_launches": n_kernels * args.steps, "kernels_per_step": n_kernels, "device_bytes": dev_bytes,
                 "clocks": clocks}
         del infer
