@@ -130,6 +130,29 @@ typedef struct vla_attn_desc {
 } vla_attn_desc;
 int vla_op_attention(const vla_attn_desc* d, void* stream);
 
+/* Y = X[tokens,K] @ W + bias as bf16, for callers that must not allocate device memory: code running inside
+ * a real-time control loop with a fixed memory budget, or on a thread that may not take the allocator's
+ * locks.  It has no counterpart in the reference (whose kernels get every buffer from PyTorch's allocator).
+ * Same tcgen05 split-K kernel as vla_op_gemm, but it calls no cudaMalloc/cudaFree or any other allocating
+ * routine: the caller provides the input, the weight ALREADY in the kernel's layout (bf16 [n_pad, k_pad],
+ * i.e. transposed to K-major and zero padded to multiples of 128 x 64) and the output, and the split-K
+ * partial tiles go to a 4 MiB scratch array that is part of the library image on every GPU.
+ *   - Shapes whose partial tiles exceed 4 MiB (split * token tiles * feature tiles * 128 * tile rows * 4 B;
+ *     e.g. more than 128 CTAs of a 64-token tile) are rejected with VLA_ERR_LIMIT.
+ *   - The first call on each device looks up the scratch address and sets kernel attributes; make that call
+ *     before any stream capture.  Later calls only enqueue the kernel on `stream` (asynchronous).
+ *   - All calls share the one scratch array: calls that can overlap on the GPU (different streams) race on it.
+ *     Calls on one stream are safe.  Nothing needs clearing between calls: every scratch element a call reads
+ *     was written earlier by the same call.  split: 0 = heuristic, else 1, 2, 4 or 8. */
+typedef struct vla_gemm_noalloc_desc {
+  const void* x; int tokens; int K;
+  const void* w_nk; int N; int n_pad; int k_pad;
+  const float* bias;
+  void* out_bf16;
+  int split;
+} vla_gemm_noalloc_desc;
+int vla_op_gemm_noalloc(const vla_gemm_noalloc_desc* d, void* stream);
+
 /* y bf16 [rows,D] = norm(x fp32 [rows,D]); mode 0 LayerNorm (w,b), 1 RMS, 2 adaRMS (w = style[3*D]); D 1024|1152|2048. */
 int vla_op_norm(const float* x, void* y, int rows, int D, int mode, const float* w, const float* b, void* stream);
 

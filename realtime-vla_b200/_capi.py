@@ -38,6 +38,12 @@ class AttnDesc(C.Structure):
                 ("scale", C.c_float), ("ksplit", C.c_int), ("iters", C.c_int), ("ms_per_iter", C.POINTER(C.c_float))]
 
 
+class GemmNoAllocDesc(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("tokens", C.c_int), ("K", C.c_int),
+                ("w_nk", C.c_void_p), ("N", C.c_int), ("n_pad", C.c_int), ("k_pad", C.c_int),
+                ("bias", C.c_void_p), ("out_bf16", C.c_void_p), ("split", C.c_int)]
+
+
 EXPORTS = {
     "vla_create": (C.c_int, [C.POINTER(VlaConfig), C.POINTER(C.c_void_p)]),
     "vla_load_weight": (C.c_int, [C.c_void_p, C.c_char_p, C.c_void_p, C.POINTER(C.c_int64), C.c_int, C.c_int]),
@@ -52,6 +58,7 @@ EXPORTS = {
     "vla_destroy": (C.c_int, [C.c_void_p]),
     "vla_last_error": (C.c_char_p, [C.c_void_p]),
     "vla_op_gemm": (C.c_int, [C.POINTER(GemmDesc), C.c_void_p]),
+    "vla_op_gemm_noalloc": (C.c_int, [C.POINTER(GemmNoAllocDesc), C.c_void_p]),
     "vla_op_attention": (C.c_int, [C.POINTER(AttnDesc), C.c_void_p]),
     "vla_op_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
 }

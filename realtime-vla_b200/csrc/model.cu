@@ -1167,6 +1167,64 @@ done:
   return rc;
 }
 
+// ---- allocation-free GEMM -----------------------------------------------------------------------------
+// Scratch for the split-K partial tiles of vla_op_gemm_noalloc: part of the library image, so it exists on
+// every GPU that loads the library from load time until exit and no call ever has to allocate it.
+#define VLA_NOALLOC_SCRATCH_FLOATS (1u << 20)   /* 4 MiB */
+static __device__ __align__(256) float vla_noalloc_scratch[VLA_NOALLOC_SCRATCH_FLOATS];
+
+int vla_op_gemm_noalloc(const vla_gemm_noalloc_desc* d, void* stream) {
+  // Device address of the scratch array, looked up once per device.  In host code the array's name is only a
+  // handle for the runtime, not a device address, so it must go through cudaGetSymbolAddress with the target
+  // device current; the result differs per device.
+  static float* scratch_of_device[64] = {nullptr};
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (!d || !d->x || !d->w_nk || !d->out_bf16) { g_last_error = "vla_op_gemm_noalloc: null argument"; return VLA_ERR_STATE; }
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { g_last_error = "vla_op_gemm_noalloc: no current device"; return VLA_ERR_CUDA; }
+  if (!scratch_of_device[dev]) {
+    float* ptr = nullptr;
+    cudaError_t ce = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), vla_noalloc_scratch);
+    if (ce != cudaSuccess || !ptr) {
+      g_last_error = std::string("vla_op_gemm_noalloc: cudaGetSymbolAddress failed: ") + cudaGetErrorString(ce);
+      return VLA_ERR_CUDA;
+    }
+    scratch_of_device[dev] = ptr;
+  }
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (d->K % 8) { g_last_error = "vla_op_gemm_noalloc: K must be a multiple of 8 (16-byte rows for TMA)"; return VLA_ERR_SHAPE; }
+  if (d->k_pad % 64 || d->n_pad % 128 || d->k_pad < d->K || d->n_pad < d->N) {
+    g_last_error = "vla_op_gemm_noalloc: w_nk must be [n_pad, k_pad] with n_pad % 128 == 0, k_pad % 64 == 0, covering N x K";
+    return VLA_ERR_SHAPE;
+  }
+  GemmEpi e;
+  memset(&e, 0, sizeof e);
+  e.kind = EPI_BF16;
+  e.act = ACT_NONE;
+  e.bias = d->bias;
+  e.out = reinterpret_cast<bf16*>(d->out_bf16);
+  e.ld_out = d->N;
+  GemmOp op;
+  std::string err;
+  if (!build_gemm(&op, reinterpret_cast<const bf16*>(d->w_nk), nullptr, d->N, d->n_pad, d->k_pad,
+                  reinterpret_cast<const bf16*>(d->x), d->tokens, d->K, d->K, e, nullptr, sms, 0, d->split, &err)) {
+    g_last_error = "vla_op_gemm_noalloc: " + err;
+    return VLA_ERR_SHAPE;
+  }
+  const size_t need = gemm_scratch_floats(op.bn, op.dual, op.grid);
+  if (need > VLA_NOALLOC_SCRATCH_FLOATS) {
+    char buf[200];
+    snprintf(buf, sizeof buf, "vla_op_gemm_noalloc: this shape needs %zu scratch floats, the built-in scratch holds %u; "
+             "use a smaller split or vla_op_gemm", need, VLA_NOALLOC_SCRATCH_FLOATS);
+    g_last_error = buf;
+    return VLA_ERR_LIMIT;
+  }
+  op.p.scratch = scratch_of_device[dev];
+  cudaError_t ce = launch_gemm(op, st, false);
+  if (ce != cudaSuccess) { g_last_error = std::string("vla_op_gemm_noalloc: launch failed: ") + cudaGetErrorString(ce); return VLA_ERR_CUDA; }
+  return VLA_OK;
+}
+
 int vla_op_norm(const float* x, void* y, int rows, int D, int mode, const float* w, const float* b, void* stream) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   cudaError_t e = launch_norm(x, D, reinterpret_cast<bf16*>(y), D, rows, D, mode, w, b, 0, 0, 0, st, false);
