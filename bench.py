@@ -230,6 +230,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--flags", type=int, default=0, help="vla_config.flags: 1 = no programmatic dependent launch, 2 = no CUDA graph")
     ap.add_argument("--microbench", action="store_true",
                     help="time only the dominant kernel of the workload (prefix GeGLU GEMM) and print its roofline object")
     ap.add_argument("--profile-forward", action="store_true",
@@ -261,7 +262,7 @@ def main():
     if wl["model"] == "pi0":
         from pi0_infer import Pi0Inference
         ck = fast_checkpoint("pi0", wl["prompt_len"], wl["seed"], device)
-        infer = Pi0Inference(ck, wl["num_views"], wl["chunk"], device=local)
+        infer = Pi0Inference(ck, wl["num_views"], wl["chunk"], device=local, flags=args.flags)
         images, state, noise = inputs(wl, device)
         step = lambda: infer.forward(images, state, noise)
         host_args = [t.cpu().pin_memory() for t in (images, state, noise)]
@@ -269,7 +270,7 @@ def main():
     else:
         from pi05_infer import Pi05Inference
         ck = fast_checkpoint("pi05", wl["prompt_len"], wl["seed"], device)
-        infer = Pi05Inference(ck, wl["num_views"], wl["chunk"], discrete_state_input=False, device=local)
+        infer = Pi05Inference(ck, wl["num_views"], wl["chunk"], discrete_state_input=False, device=local, flags=args.flags)
         images, state, noise = inputs(wl, device)
         step = lambda: infer.forward(images, noise)
         host_args = [t.cpu().pin_memory() for t in (images, noise)]

@@ -105,7 +105,7 @@ const char* vla_last_error(vla_handle h);
 
 /* Y = epilogue(X[tokens,K] @ W[K,N]) through the tcgen05 kernel.
  * epi: 0 = bf16 out (+bias, act: 0 none, 1 gelu-tanh, 2 silu, 3 GeGLU with W2), 1 = fp32 residual
- * (outf = res + bias + gate*acc, in place when res == outf), 2 = QKV+RoPE (N must be 2560; q, kcache, vcache out).
+ * (outf = res + bias + gate*acc, in place when res == outf), 2 = QKV+RoPE (N must be 2560; q, kcache, vcache out, vt = optional transposed value cache [256, vt_ld]).
  * split = cluster size along K (0 = library heuristic), bn = token tile (0 = heuristic). */
 typedef struct vla_gemm_desc {
   const void* x; int tokens; int K;
@@ -113,7 +113,7 @@ typedef struct vla_gemm_desc {
   const float* bias; int epi; int act;
   void* out_bf16; int ld_out;
   float* out_f32; const float* res; const float* gate; int res_mod;
-  void* q; void* kcache; void* vcache; int pos_off; int rows_per_obs; int kv_obs_stride; int kv_row_off;
+  void* q; void* kcache; void* vcache; void* vt; int vt_ld; int pos_off; int rows_per_obs; int kv_obs_stride; int kv_row_off;
   int split; int bn; int iters; float* ms_per_iter;
 } vla_gemm_desc;
 int vla_op_gemm(const vla_gemm_desc* d, void* stream);
@@ -129,6 +129,17 @@ typedef struct vla_attn_desc {
   float scale; int ksplit; int iters; float* ms_per_iter;
 } vla_attn_desc;
 int vla_op_attention(const vla_attn_desc* d, void* stream);
+
+/* Same attention on the tcgen05 tensor cores for head dim 256 and one group: q bf16 [n_q,256], k bf16
+ * [k_rows,256] (the first n_keys rows are used), vt bf16 [256, vt_ld] = transposed values (vt_ld % 8 == 0),
+ * o bf16 [n_q,256].  Mask rule as for vla_op_attention. */
+typedef struct vla_attn_tc_desc {
+  const void* q; const void* k; const void* vt; void* o;
+  int n_q, n_keys, k_rows, vt_ld;
+  int prefix_alloc, valid_prefix, restrict_rows;
+  float scale; int ksplit; int iters; float* ms_per_iter;
+} vla_attn_tc_desc;
+int vla_op_attention_tc(const vla_attn_tc_desc* d, void* stream);
 
 /* Y = X[tokens,K] @ W + bias as bf16, for callers that must not allocate device memory: code running inside
  * a real-time control loop with a fixed memory budget, or on a thread that may not take the allocator's

@@ -22,7 +22,7 @@ class GemmDesc(C.Structure):
                 ("bias", C.c_void_p), ("epi", C.c_int), ("act", C.c_int),
                 ("out_bf16", C.c_void_p), ("ld_out", C.c_int),
                 ("out_f32", C.c_void_p), ("res", C.c_void_p), ("gate", C.c_void_p), ("res_mod", C.c_int),
-                ("q", C.c_void_p), ("kcache", C.c_void_p), ("vcache", C.c_void_p),
+                ("q", C.c_void_p), ("kcache", C.c_void_p), ("vcache", C.c_void_p), ("vt", C.c_void_p), ("vt_ld", C.c_int),
                 ("pos_off", C.c_int), ("rows_per_obs", C.c_int), ("kv_obs_stride", C.c_int), ("kv_row_off", C.c_int),
                 ("split", C.c_int), ("bn", C.c_int), ("iters", C.c_int), ("ms_per_iter", C.POINTER(C.c_float))]
 
@@ -34,6 +34,13 @@ class AttnDesc(C.Structure):
                 ("q_go", C.c_longlong), ("q_gi", C.c_longlong), ("k_go", C.c_longlong), ("k_gi", C.c_longlong),
                 ("v_go", C.c_longlong), ("v_gi", C.c_longlong), ("o_go", C.c_longlong), ("o_gi", C.c_longlong),
                 ("n_q", C.c_int), ("n_keys", C.c_int), ("head_dim", C.c_int),
+                ("prefix_alloc", C.c_int), ("valid_prefix", C.c_int), ("restrict_rows", C.c_int),
+                ("scale", C.c_float), ("ksplit", C.c_int), ("iters", C.c_int), ("ms_per_iter", C.POINTER(C.c_float))]
+
+
+class AttnTcDesc(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("vt", C.c_void_p), ("o", C.c_void_p),
+                ("n_q", C.c_int), ("n_keys", C.c_int), ("k_rows", C.c_int), ("vt_ld", C.c_int),
                 ("prefix_alloc", C.c_int), ("valid_prefix", C.c_int), ("restrict_rows", C.c_int),
                 ("scale", C.c_float), ("ksplit", C.c_int), ("iters", C.c_int), ("ms_per_iter", C.POINTER(C.c_float))]
 
@@ -60,6 +67,7 @@ EXPORTS = {
     "vla_op_gemm": (C.c_int, [C.POINTER(GemmDesc), C.c_void_p]),
     "vla_op_gemm_noalloc": (C.c_int, [C.POINTER(GemmNoAllocDesc), C.c_void_p]),
     "vla_op_attention": (C.c_int, [C.POINTER(AttnDesc), C.c_void_p]),
+    "vla_op_attention_tc": (C.c_int, [C.POINTER(AttnTcDesc), C.c_void_p]),
     "vla_op_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
 }
 

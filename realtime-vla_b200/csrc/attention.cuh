@@ -106,8 +106,10 @@ __global__ void __launch_bounds__(128, 1) attention_kernel(const AttnParams p) {
       for (int b = 0; b < (C::HDP - HD) * 2; b += 4) *reinterpret_cast<uint32_t*>(rowp + b) = 0u;
     }
   }
-  pdl_wait();
+  KTRACE(20);
   pdl_trigger();
+  pdl_wait();
+  KTRACE(21);
 
   const int valid_prefix = p.valid_prefix_ptr ? min(max(*p.valid_prefix_ptr, 0), p.prefix_alloc) : p.valid_prefix;
 
@@ -241,6 +243,7 @@ __global__ void __launch_bounds__(128, 1) attention_kernel(const AttnParams p) {
           *reinterpret_cast<uint32_t*>(O + (size_t)i * p.ldo + d) = pack_bf16(acc[dt][h * 2] * inv, acc[dt][h * 2 + 1] * inv);
       }
     }
+    KTRACE(22);
     return;
   }
 
@@ -303,4 +306,5 @@ __global__ void __launch_bounds__(128, 1) attention_kernel(const AttnParams p) {
       }
     }
   }
+  KTRACE(22);
 }

@@ -178,6 +178,27 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 // trigger: allow the next kernel in the stream to begin its own prologue.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// ---- development timeline across kernels (-DVLA_TRACE only) ----------------------------------------------
+// Block (0,0,0) of every kernel appends (tag, %globaltimer) records; tag = kernel kind * 10 + phase
+// (0 entry, 1 dependency wait passed, 2 exit).  Compiled out of normal builds.
+#ifdef VLA_TRACE
+__device__ unsigned long long vla_ktrace[1 << 16];
+__device__ unsigned int vla_ktrace_n;
+#define KTRACE(tag) KTRACE_T(tag, 0)
+#define KTRACE_T(tag, tid) KTRACE_B(tag, tid, 0)
+#define KTRACE_B(tag, tid, bx)                                                               \
+  do {                                                                                       \
+    if (threadIdx.x == (tid) && blockIdx.x == (bx) && blockIdx.y == 0 && blockIdx.z == 0) { \
+      const unsigned int i_ = atomicAdd(&vla_ktrace_n, 1u);                                  \
+      if (i_ < (1u << 15)) { vla_ktrace[2 * i_] = (tag); vla_ktrace[2 * i_ + 1] = globaltimer_ns(); } \
+    }                                                                                        \
+  } while (0)
+#else
+#define KTRACE(tag) do {} while (0)
+#define KTRACE_T(tag, tid) do {} while (0)
+#define KTRACE_B(tag, tid, bx) do {} while (0)
+#endif
+
 // ---- math ----------------------------------------------------------------------------------------
 __device__ __forceinline__ float gelu_tanh_f(float x) {
   // x * sigmoid(2*sqrt(2/pi) * x * (1 + 0.044715 x^2))

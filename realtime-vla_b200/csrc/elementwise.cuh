@@ -15,8 +15,10 @@ __global__ void __launch_bounds__(128) norm_kernel(const float* __restrict__ x, 
                                                    int in_rpo, int in_obs_stride, int in_row_off) {
   constexpr int PER = (D + 127) / 128;
   __shared__ float red[2][4];
-  pdl_wait();
+  KTRACE(30);
   pdl_trigger();
+  pdl_wait();
+  KTRACE(31);
   const int row = blockIdx.x;
   // input row remap: output row r reads input row (r / in_rpo) * in_obs_stride + in_row_off + r % in_rpo
   const int in_row = in_rpo > 0 ? (row / in_rpo) * in_obs_stride + in_row_off + row % in_rpo : row;
@@ -61,13 +63,14 @@ __global__ void __launch_bounds__(128) norm_kernel(const float* __restrict__ x, 
     else o = v[i] * rstd * (1.0f + w[d]) + w[D + d];
     yr[d] = __float2bfloat16(o);
   }
+  KTRACE(32);
 }
 
 // images bf16 (nv,224,224,3) -> patches bf16 [nv*256, 640]: row = view*256 + py*16 + px, column =
 // (iy*14 + ix)*3 + c for the 14x14x3 patch, columns 588..639 zero.
 __global__ void patchify_kernel(const bf16* __restrict__ img, bf16* __restrict__ out, int n_rows) {
-  pdl_wait();
   pdl_trigger();
+  pdl_wait();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n_rows * 640) return;
   const int row = idx / 640, col = idx - row * 640;
@@ -96,14 +99,14 @@ __global__ void repack_kn_to_nk(const bf16* __restrict__ w, int K, int N, bf16* 
 }
 
 __global__ void bf16_to_f32_kernel(const bf16* __restrict__ in, float* __restrict__ out, size_t n, float scale) {
-  pdl_wait();
   pdl_trigger();
+  pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) out[i] = __bfloat162float(in[i]) * scale;
 }
 __global__ void f32_to_bf16_kernel(const float* __restrict__ in, bf16* __restrict__ out, size_t n) {
-  pdl_wait();
   pdl_trigger();
+  pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) out[i] = __float2bfloat16(in[i]);
 }
@@ -114,15 +117,15 @@ __global__ void scale_bf16_kernel(bf16* __restrict__ w, size_t n, float scale) {
 }
 // Start of the action-expert stage: fp32 copy of the bf16 noise, and (Pi0) nothing else.
 __global__ void noise_init_kernel(const bf16* __restrict__ noise, float* __restrict__ noise_f32, int n) {
-  pdl_wait();
   pdl_trigger();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) noise_f32[i] = __bfloat162float(noise[i]);
 }
 // prompt embeddings bf16 [L,2048] -> fp32 residual stream rows obs*P + row_off + i, for every observation
 __global__ void prompt_rows_kernel(const bf16* __restrict__ emb, float* __restrict__ x, int L, int P, int row_off, int batch) {
-  pdl_wait();
   pdl_trigger();
+  pdl_wait();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t per = (size_t)L * 2048;
   if (idx >= per * batch) return;
@@ -133,8 +136,8 @@ __global__ void prompt_rows_kernel(const bf16* __restrict__ emb, float* __restri
 // dst rows (b*dst_stride + dst_off) <- src rows b, fp32, `width` columns
 __global__ void copy_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, int width, int dst_stride_rows,
                                  int dst_off_rows, int batch) {
-  pdl_wait();
   pdl_trigger();
+  pdl_wait();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= width * batch) return;
   const int b = idx / width, c = idx - b * width;

@@ -43,6 +43,8 @@ struct GemmEpi {
   bf16* q;
   bf16* kc;
   bf16* vc;
+  bf16* vt;               // optional transposed value cache [observation][256][vt_ld] (read by the tcgen05 attention)
+  int vt_ld;
   const float* rope_cos;  // [pos][128]
   const float* rope_sin;
   const int* pos_base;    // optional device scalar added to the position
@@ -191,7 +193,10 @@ __device__ __forceinline__ void gemm_epilogue_cols(const GemmEpi& e, const EpiTh
           const int obs = t / e.rows_per_obs, r = t - obs * e.rows_per_obs;
           const size_t row = (size_t)obs * e.kv_obs_stride + e.kv_row_off + r;
           if (n < 2304) e.kc[row * 256 + (n - 2048)] = o;
-          else e.vc[row * 256 + (n - 2304)] = o;
+          else {
+            e.vc[row * 256 + (n - 2304)] = o;
+            if (e.vt) e.vt[((size_t)obs * 256 + (n - 2304)) * e.vt_ld + e.kv_row_off + r] = o;
+          }
         }
       }
     }
@@ -216,6 +221,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  KTRACE(10);
   if (threadIdx.x == 0) GEMM_TRACE(0);
   const int split = SPLITK ? p.split : 1;
   const int rank = SPLITK ? (int)blockIdx.x : 0;  // == cluster rank: cluster dims are (split,1,1), gridDim.x == split
@@ -246,24 +252,41 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) GEMM_TRACE(1);
 
-  // Everything above is independent of the previous kernel's output.
-  pdl_wait();
+  // Let the next kernels of the stream start now: their prologue and weight prefetch run under this kernel
+  // (they block in their own griddepcontrol.wait until this grid has completed).
   pdl_trigger();
+  // Weights do not depend on the previous kernel: fill the pipeline with weight tiles before waiting for it.
+  const int n_pre = n_iters < C::STAGES ? n_iters : C::STAGES;
+  uint64_t pol_w = 0;
+  if (warp == 0 && lane == 0) {
+    pol_w = policy_evict_first();
+    for (int it = 0; it < n_pre; ++it) {
+      const uint32_t st = smem_base + it * C::STAGE_BYTES;
+      const int k0 = (kb_begin + it) * 64;
+      mbar_expect_tx(full_bar + 8 * it, C::STAGE_BYTES);
+      tma_load_2d(st, &p.tmA, full_bar + 8 * it, k0, feat0, pol_w);
+      if (DUAL) tma_load_2d(st + C::A_BYTES, &p.tmA2, full_bar + 8 * it, k0, feat0, pol_w);
+    }
+  }
+  // Activations (and everything the epilogue reads or writes) do.
+  pdl_wait();
+  KTRACE(11);
   if (threadIdx.x == 0) GEMM_TRACE(2);
 
   if (warp == 0) {
     if (lane == 0) {
-      const uint64_t pol_w = policy_evict_first();
       const uint64_t pol_x = policy_evict_last();
       for (int it = 0; it < n_iters; ++it) {
         const int s = it % C::STAGES;
-        const uint32_t ph = (uint32_t)(it / C::STAGES) & 1u;
-        if (!mbar_wait(empty_bar + 8 * s, ph ^ 1u, abort_flag)) break;
         const uint32_t st = smem_base + s * C::STAGE_BYTES;
         const int k0 = (kb_begin + it) * 64;
-        mbar_expect_tx(full_bar + 8 * s, C::STAGE_BYTES);
-        tma_load_2d(st, &p.tmA, full_bar + 8 * s, k0, feat0, pol_w);
-        if (DUAL) tma_load_2d(st + C::A_BYTES, &p.tmA2, full_bar + 8 * s, k0, feat0, pol_w);
+        if (it >= n_pre) {
+          const uint32_t ph = (uint32_t)(it / C::STAGES) & 1u;
+          if (!mbar_wait(empty_bar + 8 * s, ph ^ 1u, abort_flag)) break;
+          mbar_expect_tx(full_bar + 8 * s, C::STAGE_BYTES);
+          tma_load_2d(st, &p.tmA, full_bar + 8 * s, k0, feat0, pol_w);
+          if (DUAL) tma_load_2d(st + C::A_BYTES, &p.tmA2, full_bar + 8 * s, k0, feat0, pol_w);
+        }
         tma_load_2d(st + C::A_BYTES * (DUAL ? 2 : 1), &p.tmB, full_bar + 8 * s, k0, tok0, pol_x);
       }
       GEMM_TRACE(3);
@@ -281,6 +304,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         if (!ok) break;
         tc_fence_after();
         if (it == 0) GEMM_TRACE(4);
+        if (it == 0) KTRACE_T(17, 32);
         const uint32_t st = smem_base + s * C::STAGE_BYTES;
         const uint64_t da = umma_desc_sw128(st);
         const uint64_t da2 = umma_desc_sw128(st + C::A_BYTES);
@@ -314,9 +338,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   th.pos_base = (p.epi.kind == EPI_QKV && p.epi.pos_base) ? *p.epi.pos_base : 0;
   bool acc_ok = false;
   if (is_epi) {
-    acc_ok = mbar_wait(tmem_full_bar, 0, abort_flag);
+    acc_ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar, 0, abort_flag));   // TMEM loads are warp-collective
     tc_fence_after();
     if (threadIdx.x == 64) GEMM_TRACE(6);
+    KTRACE_T(13, 64);
   }
   const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
 
@@ -353,8 +378,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     }
     __syncwarp();
     if (threadIdx.x == 64) GEMM_TRACE(7);
+    KTRACE_T(14, 64);
     cluster_sync_all();   // release/acquire at cluster scope: every partial tile of the cluster is visible
     if (threadIdx.x == 64) GEMM_TRACE(8);
+    KTRACE_T(15, 64);
     if (is_epi) {
       // this CTA owns columns rank, rank+split, ...; the two warps of a quarter alternate groups of 4 of them
       const int n_owned = n_cols > rank ? (n_cols - rank + split - 1) / split : 0;
@@ -381,6 +408,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       }
     }
     if (threadIdx.x == 64) GEMM_TRACE(9);
+    KTRACE_T(16, 64);
   }
 
   // ---------------- teardown ----------------
@@ -393,5 +421,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     for (int i = 0; i < 32; ++i) __nanosleep(1000);   // let any copy still in flight land before the CTA exits
   }
   if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+  KTRACE(12);
   if (threadIdx.x == 32) GEMM_TRACE(13);
 }

@@ -18,6 +18,7 @@
 
 #include "../../include/vla_b200.h"
 #include "attention.cuh"
+#include "attention_tc.cuh"
 #include "elementwise.cuh"
 #include "gemm_sm100.cuh"
 
@@ -114,8 +115,10 @@ size_t gemm_scratch_floats(int bn, bool dual, dim3 grid) {
 
 int pick_split(int units, int k_blocks, int sm_count) {
   int split = 1;
-  // clusters of 8 fit about 16 at a time on 148 SMs (8 GPCs), so stay at or below 128 CTAs when splitting
-  while (split < 8 && units * split * 2 <= (sm_count * 7) / 8 && split * 2 <= k_blocks) split *= 2;
+  // Split only up to about half of the SMs: consecutive kernels overlap through programmatic dependent
+  // launch (the next kernel prefetches its weights on the SMs this one leaves free), and clusters of 8 fit
+  // only ~16 at a time on the 8 GPCs anyway.
+  while (split < 8 && units * split * 2 <= (sm_count * 9) / 16 && split * 2 <= k_blocks) split *= 2;
   return split;
 }
 
@@ -222,6 +225,46 @@ int pick_ksplit(int n_q, int n_keys, int groups, int sm_count) {
   return ks;
 }
 
+// ---- tcgen05 attention (head dim 256, one group) ---------------------------------------------------
+struct AttnTcOp {
+  AttnTcParams p;
+  dim3 grid;
+};
+int pick_ksplit_tc(int n_q, int n_keys, int sm_count) {
+  const int row_blocks = (n_q + 127) / 128, chunks = (n_keys + 127) / 128;
+  int ks = 1;
+  while (ks < 8 && ks < chunks && row_blocks * ks * 2 <= sm_count) ks *= 2;
+  return ks;
+}
+size_t attn_tc_scratch_floats(int n_q, int ksplit) {
+  return ksplit > 1 ? (size_t)((n_q + 127) / 128) * ksplit * 128 * AttnTcCfg::SCOLS : 0;
+}
+// q [n_q,256]; k [k_rows,256] (n_keys <= k_rows used); vt [256, vt_ld] transposed values
+bool build_attn_tc(AttnTcOp* op, const bf16* q, const bf16* k, int k_rows, const bf16* vt, int vt_ld, bf16* o, int ldo, int n_q,
+                   int n_keys, int prefix_alloc, int valid_prefix, const int* valid_ptr, int restrict_rows, float scale,
+                   int ksplit, float* scratch, int* status, std::string* err) {
+  memset(op, 0, sizeof *op);
+  if (vt_ld % 8) { *err = "transposed value cache pitch must be a multiple of 8"; return false; }
+  if (!make_tmap(&op->p.tmQ, q, 256, n_q, 256, 128, err)) return false;
+  if (!make_tmap(&op->p.tmK, k, 256, k_rows, 256, 128, err)) return false;
+  if (!make_tmap(&op->p.tmVt, vt, vt_ld, 256, vt_ld, 256, err)) return false;
+  op->p.o = o; op->p.ldo = ldo; op->p.n_q = n_q; op->p.n_keys = n_keys;
+  op->p.prefix_alloc = prefix_alloc; op->p.valid_prefix = valid_prefix; op->p.valid_prefix_ptr = valid_ptr;
+  op->p.restrict_rows = restrict_rows; op->p.scale_log2e = scale * 1.4426950408889634f;
+  op->p.ksplit = ksplit; op->p.scratch = scratch; op->p.status = status;
+  op->grid = dim3(ksplit, (n_q + 127) / 128, 1);
+  return true;
+}
+cudaError_t launch_attn_tc(const AttnTcOp& op, cudaStream_t st, bool pdl) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnTcCfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  return launch_ex(attention_tc_kernel, op.grid, dim3(AttnTcCfg::THREADS), AttnTcCfg::SMEM_BYTES, st, op.p.ksplit, pdl, op.p);
+}
+
 cudaError_t launch_norm(const float* x, int ld_x, bf16* y, int ld_y, int rows, int D, int mode, const float* w,
                         const float* b, int in_rpo, int in_stride, int in_off, cudaStream_t st, bool pdl) {
   if (D == 1152) return launch_ex(norm_kernel<1152>, dim3(rows), dim3(128), 0, st, 1, pdl, x, ld_x, y, ld_y, mode, w, b, in_rpo, in_stride, in_off);
@@ -273,7 +316,8 @@ struct vla_model {
   float* vision_x;
   float* encoder_x;
   bf16 *encoder_xn, *encoder_q, *encoder_attn, *encoder_hidden;
-  bf16 *kcache, *vcache;
+  bf16 *kcache, *vcache, *vtcache;
+  int T_pad;
   float *decoder_x, *state_tok;
   bf16 *decoder_xn, *decoder_q, *decoder_attn, *decoder_hidden, *decoder_act, *decoder_xfin;
   bf16* lang;
@@ -427,6 +471,8 @@ bool alloc_buffers(vla_model* m) {
   ok &= m->dalloc(&m->encoder_hidden, Np * 16384);
   ok &= m->dalloc(&m->kcache, (size_t)m->nl * B * m->T * 256, "encoder_K");
   ok &= m->dalloc(&m->vcache, (size_t)m->nl * B * m->T * 256, "encoder_V");
+  m->T_pad = round_up(m->T, 8);
+  ok &= m->dalloc(&m->vtcache, (size_t)m->nl * B * 256 * m->T_pad);
   ok &= m->dalloc(&m->decoder_x, Ns * 1024, "decoder_x");
   ok &= m->dalloc(&m->state_tok, B * 1024);
   ok &= m->dalloc(&m->decoder_xn, Ns * 1024);
@@ -499,6 +545,20 @@ struct Plan {
             int in_stride = 0, int in_off = 0) {
     const bool pdl = m->use_pdl;
     kernel([=](cudaStream_t st) { return launch_norm(x, D, y, D, rows, D, mode, w, b, in_rpo, in_stride, in_off, st, pdl); });
+  }
+  void attention_tc(const bf16* q, const bf16* k, const bf16* vt, bf16* o, int n_q, int n_keys, const int* valid_ptr,
+                    int restrict_rows) {
+    if (!ok) return;
+    AttnTcOp op;
+    const int ks = pick_ksplit_tc(n_q, n_keys, m->sm_count);
+    if (attn_tc_scratch_floats(n_q, ks) > m->attn_scratch_cap) { ok = false; err = "attention scratch too small"; return; }
+    if (!build_attn_tc(&op, q, k, m->T, vt, m->T_pad, o, 256, n_q, n_keys, m->P, m->P, valid_ptr, restrict_rows, 1.0f / 16.0f,
+                       ks, m->attn_scratch, m->d_status, &err)) {
+      ok = false;
+      return;
+    }
+    const bool pdl = m->use_pdl;
+    kernel([op, pdl](cudaStream_t st) { return launch_attn_tc(op, st, pdl); });
   }
   void attention(AttnParams p, int head_dim, int groups) {
     const bool pdl = m->use_pdl;
@@ -578,9 +638,11 @@ void plan_prefix(Plan& pl) {
   for (int l = 0; l < m->nl; ++l) {  // pi0_infer.py:851-884, pi05_infer.py:321-380
     bf16* kc = m->kcache + (size_t)l * m->B * m->T * 256;
     bf16* vc = m->vcache + (size_t)l * m->B * m->T * 256;
+    bf16* vt = m->vtcache + (size_t)l * m->B * 256 * m->T_pad;
     pl.norm(m->encoder_x, m->encoder_xn, Np, 2048, NORM_RMS, nullptr, nullptr);
     GemmEpi e = pl.epi0();
     e.kind = EPI_QKV; e.q = m->encoder_q; e.kc = kc; e.vc = vc; e.rope_cos = m->rope_cos; e.rope_sin = m->rope_sin;
+    e.vt = vt; e.vt_ld = m->T_pad;
     e.pos_off = 0; e.rows_per_obs = m->P; e.kv_obs_stride = m->T; e.kv_row_off = 0;
     pl.gemm("encoder_attn_qkv_w", nullptr, l, m->encoder_xn, Np, 2048, 2048, e);
     if (l == m->nl - 1) break;   // the last prefix layer only feeds the cache
@@ -591,7 +653,8 @@ void plan_prefix(Plan& pl) {
     a.g_inner = 1; a.n_q = m->P * 8; a.n_keys = m->P; a.prefix_alloc = m->P; a.valid_prefix = m->P;
     a.valid_prefix_ptr = m->pi05 ? m->d_valid_len : nullptr;
     a.scale_log2e = 1.4426950408889634f / 16.f;
-    pl.attention(a, 256, m->B);
+    if (m->B == 1) pl.attention_tc(m->encoder_q, kc, vt, m->encoder_attn, m->P * 8, m->P, m->pi05 ? m->d_valid_len : nullptr, 0);
+    else pl.attention(a, 256, m->B);
     e = pl.epi0();
     e.kind = EPI_RESID; e.outf = m->encoder_x; e.ld_outf = 2048; e.res_in = m->encoder_x; e.ld_res = 2048;
     pl.gemm("encoder_attn_o_w", nullptr, l, m->encoder_attn, Np, 2048, 2048, e);
@@ -643,6 +706,7 @@ void plan_decoder(Plan& pl) {
     for (int l = 0; l < m->nl; ++l) {  // pi0_infer.py:1186-1223, pi05_infer.py:427-509
       bf16* kc = m->kcache + (size_t)l * B * m->T * 256;
       bf16* vc = m->vcache + (size_t)l * B * m->T * 256;
+      bf16* vt = m->vtcache + (size_t)l * B * 256 * m->T_pad;
       const float* st_attn = pi05 ? m->style_attn + ((size_t)step * m->nl + l) * 3072 : nullptr;
       const float* st_ffn = pi05 ? m->style_ffn + ((size_t)step * m->nl + l) * 3072 : nullptr;
       pl.norm(m->decoder_x, m->decoder_xn, Ns, 1024, pi05 ? NORM_ADARMS : NORM_RMS, st_attn, nullptr);
@@ -650,6 +714,7 @@ void plan_decoder(Plan& pl) {
       e.kind = EPI_QKV; e.q = m->decoder_q; e.kc = kc; e.vc = vc; e.rope_cos = m->rope_cos; e.rope_sin = m->rope_sin;
       e.pos_off = pi05 ? 0 : m->P; e.pos_base = pi05 ? m->d_pos_base : nullptr;
       e.rows_per_obs = S; e.kv_obs_stride = m->T; e.kv_row_off = m->P;
+      e.vt = vt; e.vt_ld = m->T_pad;
       pl.gemm("decoder_attn_qkv_w", nullptr, l, m->decoder_xn, Ns, 1024, 1024, e);
       AttnParams a; memset(&a, 0, sizeof a);
       a.q = m->decoder_q; a.k = kc; a.v = vc; a.o = m->decoder_attn;
@@ -659,7 +724,8 @@ void plan_decoder(Plan& pl) {
       a.valid_prefix_ptr = pi05 ? m->d_valid_len : nullptr;
       a.restrict_rows = pi05 ? 0 : 8;
       a.scale_log2e = 1.4426950408889634f / 16.f;
-      pl.attention(a, 256, B);
+      if (B == 1) pl.attention_tc(m->decoder_q, kc, vt, m->decoder_attn, S * 8, m->T, pi05 ? m->d_valid_len : nullptr, pi05 ? 0 : 8);
+      else pl.attention(a, 256, B);
       e = pl.epi0();
       e.kind = EPI_RESID; e.outf = m->decoder_x; e.ld_outf = 1024; e.res_in = m->decoder_x; e.ld_res = 1024;
       e.gate = pi05 ? st_attn + 2048 : nullptr;
@@ -1067,6 +1133,7 @@ int vla_op_gemm(const vla_gemm_desc* d, void* stream) {
     e.q = reinterpret_cast<bf16*>(d->q); e.kc = reinterpret_cast<bf16*>(d->kcache); e.vc = reinterpret_cast<bf16*>(d->vcache);
     e.rope_cos = cosT; e.rope_sin = sinT; e.pos_off = d->pos_off; e.rows_per_obs = d->rows_per_obs;
     e.kv_obs_stride = d->kv_obs_stride; e.kv_row_off = d->kv_row_off;
+    e.vt = reinterpret_cast<bf16*>(d->vt); e.vt_ld = d->vt_ld;
   }
   if (!build_gemm(&op, wt, wt2, d->N, Np, Kp, reinterpret_cast<const bf16*>(d->x), d->tokens, d->K, d->K, e, status, sms,
                   d->bn, d->split, &err)) {
@@ -1223,6 +1290,69 @@ int vla_op_gemm_noalloc(const vla_gemm_noalloc_desc* d, void* stream) {
   cudaError_t ce = launch_gemm(op, st, false);
   if (ce != cudaSuccess) { g_last_error = std::string("vla_op_gemm_noalloc: launch failed: ") + cudaGetErrorString(ce); return VLA_ERR_CUDA; }
   return VLA_OK;
+}
+
+#ifdef VLA_TRACE
+// development only: copy out and reset the cross-kernel timeline
+int vla_ktrace_dump(unsigned long long* out, int max_records) {
+  unsigned int n = 0;
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(&n, vla_ktrace_n, sizeof n);
+  if ((int)n > max_records) n = max_records;
+  cudaMemcpyFromSymbol(out, vla_ktrace, (size_t)n * 16);
+  unsigned int zero = 0;
+  cudaMemcpyToSymbol(vla_ktrace_n, &zero, sizeof zero);
+  return (int)n;
+}
+#endif
+
+int vla_op_attention_tc(const vla_attn_tc_desc* d, void* stream) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int rc = VLA_OK;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  float* scratch = nullptr;
+  int* status = nullptr;
+  int dev = 0, sms = 148;
+  AttnTcOp op;
+  std::string err;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int ks = d->ksplit > 0 ? d->ksplit : pick_ksplit_tc(d->n_q, d->n_keys, sms);
+  if (ks > 8 || (ks & (ks - 1))) { g_last_error = "ksplit must be 1, 2, 4 or 8"; return VLA_ERR_SHAPE; }
+  CKG(cudaMalloc(&status, 4));
+  CKG(cudaMemsetAsync(status, 0, 4, st));
+  if (ks > 1) CKG(cudaMalloc(&scratch, attn_tc_scratch_floats(d->n_q, ks) * sizeof(float)));
+  if (!build_attn_tc(&op, reinterpret_cast<const bf16*>(d->q), reinterpret_cast<const bf16*>(d->k), d->k_rows,
+                     reinterpret_cast<const bf16*>(d->vt), d->vt_ld, reinterpret_cast<bf16*>(d->o), 256, d->n_q, d->n_keys,
+                     d->prefix_alloc, d->valid_prefix, nullptr, d->restrict_rows, d->scale, ks, scratch, status, &err)) {
+    g_last_error = err;
+    rc = VLA_ERR_SHAPE;
+    goto done;
+  }
+  CKG(launch_attn_tc(op, st, false));
+  CKG(cudaStreamSynchronize(st));
+  if (d->iters > 0 && d->ms_per_iter) {
+    CKG(cudaEventCreate(&e0));
+    CKG(cudaEventCreate(&e1));
+    CKG(cudaEventRecord(e0, st));
+    for (int i = 0; i < d->iters; ++i) CKG(launch_attn_tc(op, st, false));
+    CKG(cudaEventRecord(e1, st));
+    CKG(cudaStreamSynchronize(st));
+    float ms = 0.f;
+    CKG(cudaEventElapsedTime(&ms, e0, e1));
+    *d->ms_per_iter = ms / d->iters;
+  }
+  {
+    int w = 0;
+    CKG(cudaMemcpy(&w, status, 4, cudaMemcpyDeviceToHost));
+    if (w) { g_last_error = "device status word raised: bounded wait timed out"; rc = VLA_ERR_DEVICE; }
+  }
+done:
+  if (e0) cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  cudaFree(scratch);
+  cudaFree(status);
+  return rc;
 }
 
 int vla_op_norm(const float* x, void* y, int rows, int D, int mode, const float* w, const float* b, void* stream) {

@@ -37,10 +37,12 @@ def gemm(x, w, *, w2=None, bias=None, epi=0, act=0, res=None, gate=None, res_mod
         rows = qkv["kv_rows"]
         kc = torch.zeros(rows, 256, dtype=torch.bfloat16, device=x.device)
         vc = torch.zeros(rows, 256, dtype=torch.bfloat16, device=x.device)
-        d.q, d.kcache, d.vcache = _p(q), _p(kc), _p(vc)
+        vt_ld = (rows + 7) // 8 * 8
+        vt = torch.zeros(256, vt_ld, dtype=torch.bfloat16, device=x.device)
+        d.q, d.kcache, d.vcache, d.vt, d.vt_ld = _p(q), _p(kc), _p(vc), _p(vt), vt_ld
         d.pos_off, d.rows_per_obs = qkv["pos_off"], qkv["rows_per_obs"]
         d.kv_obs_stride, d.kv_row_off = qkv["kv_obs_stride"], qkv["kv_row_off"]
-        out = (q, kc, vc)
+        out = (q, kc, vc, vt)
     rc = lib.vla_op_gemm(C.byref(d), None)
     _capi.check(rc)
     torch.cuda.synchronize()
@@ -64,6 +66,28 @@ def attention(q, k, v, *, ldq, ldk, ldv, ldo, o, groups_outer=1, groups_inner=1,
     _capi.check(lib.vla_op_attention(C.byref(d), None))
     torch.cuda.synchronize()
     return ms.value
+
+
+def attention_tc(q, k, v, *, n_keys=None, prefix_alloc=None, valid_prefix=None, restrict_rows=0, scale, ksplit=0, iters=0):
+    """tcgen05 attention: q [n_q,256], k/v [k_rows,256] bf16 (v is transposed here into the layout the kernel reads)."""
+    lib = _capi.lib()
+    n_q, k_rows = q.shape[0], k.shape[0]
+    n_keys = k_rows if n_keys is None else n_keys
+    vt_ld = (k_rows + 7) // 8 * 8
+    vt = torch.zeros(256, vt_ld, dtype=torch.bfloat16, device=q.device)
+    vt[:, :k_rows] = v.t()
+    o = torch.zeros(n_q, 256, dtype=torch.bfloat16, device=q.device)
+    d = _capi.AttnTcDesc()
+    d.q, d.k, d.vt, d.o = _p(q), _p(k), _p(vt), _p(o)
+    d.n_q, d.n_keys, d.k_rows, d.vt_ld = n_q, n_keys, k_rows, vt_ld
+    d.prefix_alloc = n_keys if prefix_alloc is None else prefix_alloc
+    d.valid_prefix = d.prefix_alloc if valid_prefix is None else valid_prefix
+    d.restrict_rows, d.scale, d.ksplit, d.iters = restrict_rows, scale, ksplit, iters
+    ms = C.c_float(0)
+    d.ms_per_iter = C.pointer(ms)
+    _capi.check(lib.vla_op_attention_tc(C.byref(d), None))
+    torch.cuda.synchronize()
+    return (o, ms.value) if iters else o
 
 
 def norm(x, mode, w=None, b=None):

@@ -101,6 +101,32 @@ def test_attention_suffix(P, S, valid, restrict, ksplit):
     assert_close(o, ref_attention(q, k, v, 1 / 16, mask), what="suffix attention")
 
 
+@pytest.mark.parametrize("P,valid,ksplit", [(256, 256, 1), (256, 256, 2), (300, 277, 0), (788, 788, 0), (788, 788, 1), (20, 20, 1),
+                                            (564, 540, 4)])
+def test_attention_tc_prefix(P, valid, ksplit):
+    import vla_ops
+    d = dev()
+    q, k, v = rnd((P * 8, 256), 1.0, 6, d), rnd((P + 51, 256), 1.0, 7, d), rnd((P + 51, 256), 1.0, 8, d)
+    o = vla_ops.attention_tc(q, k, v, n_keys=P, prefix_alloc=P, valid_prefix=valid, scale=1 / 16, ksplit=ksplit)
+    mask = torch.ones(P * 8, P, dtype=torch.bool, device=d)
+    mask[:, valid:] = False
+    assert_close(o, ref_attention(q, k[:P], v[:P], 1 / 16, mask), what="tcgen05 prefix attention")
+
+
+@pytest.mark.parametrize("P,S,valid,restrict,ksplit", [(256, 51, 256, 8, 0), (788, 51, 788, 8, 0), (788, 51, 788, 8, 2),
+                                                       (564, 50, 540, 0, 4), (6, 4, 6, 8, 1), (788, 51, 788, 8, 1)])
+def test_attention_tc_suffix(P, S, valid, restrict, ksplit):
+    import vla_ops
+    d = dev()
+    T = P + S
+    q, k, v = rnd((S * 8, 256), 1.0, 9, d), rnd((T, 256), 1.0, 10, d), rnd((T, 256), 1.0, 11, d)
+    o = vla_ops.attention_tc(q, k, v, prefix_alloc=P, valid_prefix=valid, restrict_rows=restrict, scale=1 / 16, ksplit=ksplit)
+    mask = torch.ones(S * 8, T, dtype=torch.bool, device=d)
+    mask[:, valid:P] = False
+    mask[:restrict, P + 1:] = False
+    assert_close(o, ref_attention(q, k, v, 1 / 16, mask), what="tcgen05 suffix attention")
+
+
 # ---------------------------------------------------------------------------------------------------
 GEMM_CASES = [
     # tokens, K, N, split, bn
@@ -170,7 +196,7 @@ def test_gemm_qkv_rope(tokens, K, pos_off, split):
     d = dev()
     x, w = rnd((tokens, K), 1.0, 29, d), rnd((K, 2560), 0.03, 30, d)
     row_off = pos_off
-    q, kc, vc = gpu_ops.gemm(x, w, epi=2, split=split,
+    q, kc, vc, vt = gpu_ops.gemm(x, w, epi=2, split=split,
                              qkv=dict(kv_rows=row_off + tokens, pos_off=pos_off, rows_per_obs=tokens,
                                       kv_obs_stride=row_off + tokens, kv_row_off=row_off))
     y = x.float() @ w.float()
@@ -180,4 +206,5 @@ def test_gemm_qkv_rope(tokens, K, pos_off, split):
     assert_close(q, qr, what="Q")
     assert_close(kc[row_off:], kr, what="K")
     assert_close(vc[row_off:], y[:, 2304:], what="V")
+    assert_close(vt[:, row_off:row_off + tokens].t(), y[:, 2304:], what="V transposed")
     assert kc[:row_off].abs().max().item() == 0 if row_off else True
