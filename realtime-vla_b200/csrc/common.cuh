@@ -75,6 +75,21 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tm, uint32
       ::"r"(dst), "l"(tm), "r"(bar), "r"(c0), "r"(c1), "l"(policy)
       : "memory");
 }
+// shared -> global tile store / fp32 reduce-add through TMA (bulk async-group completion)
+__device__ __forceinline__ void tma_store_2d(const void* tm, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(tm), "r"(src), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const void* tm, uint32_t src, int c0, int c1) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(tm), "r"(src), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 __device__ __forceinline__ uint64_t policy_evict_first() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
@@ -200,9 +215,20 @@ __device__ unsigned int vla_ktrace_n;
 #endif
 
 // ---- math ----------------------------------------------------------------------------------------
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// x * sigmoid(u) = 0.5 x (1 + tanh(u/2)): one special-function op per element instead of two (ex2 + rcp);
+// the epilogues of the MLP GEMMs are bound by the special-function unit.
 __device__ __forceinline__ float gelu_tanh_f(float x) {
   // x * sigmoid(2*sqrt(2/pi) * x * (1 + 0.044715 x^2))
-  const float u = 1.5957691216057308f * x * (1.0f + 0.044715f * x * x);
-  return __fdividef(x, 1.0f + __expf(-u));
+  const float u = 0.7978845608028654f * x * (1.0f + 0.044715f * x * x);
+  const float hx = 0.5f * x;
+  return hx + hx * tanh_approx(u);
 }
-__device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) {
+  const float hx = 0.5f * x;
+  return hx + hx * tanh_approx(hx);
+}

@@ -69,6 +69,9 @@ struct GemmParams {
   CUtensorMap tmA;   // weights [features_padded, Kp], box 64 x 128
   CUtensorMap tmA2;  // second weight (GeGLU "up"), only for DUAL
   CUtensorMap tmB;   // activations [tokens, K], box 64 x BN
+  CUtensorMap tmOut; // output [tokens, features], box 32 x 32, no swizzle (see out_mode)
+  int out_mode;      // 0: epilogue stores with plain st.global; 1: bf16 tile stores through TMA; 2: fp32 tile stores;
+                     // 3: fp32 tile reduce-add (in-place residual: x += gate*acc + bias, one add per element)
   int n_feat;        // valid features
   int n_tok;         // valid tokens
   int k_blocks;      // Kp / 64
@@ -137,19 +140,38 @@ __device__ __forceinline__ void gemm_epilogue_cols(const GemmEpi& e, const EpiTh
     }
     bf16* o = e.out + (size_t)t0 * e.ld_out + n;
     const size_t step = (size_t)tstride * e.ld_out;
+#if defined(VLA_EPI_EXPERIMENT) && VLA_EPI_EXPERIMENT == 1
+    float acc_ = 0.f;
+#pragma unroll
+    for (int j = 0; j < NC; ++j) acc_ += x[j];
+    if (n_valid > 0) o[0] = __float2bfloat16(acc_);
+#else
 #pragma unroll
     for (int j = 0; j < NC; ++j)
       if (j < n_valid) o[j * step] = __float2bfloat16(x[j]);
+#endif
   } else if (e.kind == EPI_RESID) {
     if (!th.n_ok) return;
+    // Row bookkeeping without per-column integer division (an emulated division per column made this epilogue
+    // 3x slower than its memory traffic): one division for the first column, then incremental wrap-around.
     float r[NC];
     size_t orow[NC];
+    int o_obs = 0, o_r = t0, m_r = t0;
+    if (e.out_rpo > 0 && t0 >= e.out_rpo) { o_obs = t0 / e.out_rpo; o_r = t0 - o_obs * e.out_rpo; }
+    if (e.res_mod > 0 && t0 >= e.res_mod) m_r = t0 % e.res_mod;
 #pragma unroll
     for (int j = 0; j < NC; ++j) {
+      orow[j] = e.out_rpo > 0 ? (size_t)o_obs * e.out_obs_stride + o_r : (size_t)(t0 + j * tstride);
       r[j] = 0.f;
-      const int t = t0 + j * tstride;
-      orow[j] = e.out_rpo > 0 ? (size_t)(t / e.out_rpo) * e.out_obs_stride + t % e.out_rpo : (size_t)t;
-      if (j < n_valid && e.res_in) r[j] = e.res_in[(size_t)(e.res_mod > 0 ? t % e.res_mod : (int)orow[j]) * e.ld_res + n];
+      if (j < n_valid && e.res_in) r[j] = e.res_in[(e.res_mod > 0 ? (size_t)m_r : orow[j]) * e.ld_res + n];
+      if (e.out_rpo > 0) {
+        o_r += tstride;
+        if (o_r >= e.out_rpo) { o_r -= e.out_rpo; ++o_obs; }
+      }
+      if (e.res_mod > 0) {
+        m_r += tstride;
+        if (m_r >= e.res_mod) m_r -= e.res_mod;
+      }
     }
 #pragma unroll
     for (int j = 0; j < NC; ++j) r[j] += v[j] * th.gate + th.bias;
@@ -162,18 +184,24 @@ __device__ __forceinline__ void gemm_epilogue_cols(const GemmEpi& e, const EpiTh
     }
   } else {  // EPI_QKV
     float c[NC], s[NC];
+    int lrow[NC], lobs[NC];
     const int i = (n & 255) >> 1;
     const bool rot = n < 2304;
+    int obs = 0, rr = t0;
+    if (t0 >= e.rows_per_obs) { obs = t0 / e.rows_per_obs; rr = t0 - obs * e.rows_per_obs; }
 #pragma unroll
     for (int j = 0; j < NC; ++j) {
+      lrow[j] = rr;
+      lobs[j] = obs;
       c[j] = 1.f;
       s[j] = 0.f;
       if (j < n_valid && rot) {
-        const int t = t0 + j * tstride;
-        const int pos = t % e.rows_per_obs + e.pos_off + th.pos_base;
+        const int pos = rr + e.pos_off + th.pos_base;
         c[j] = e.rope_cos[pos * 128 + i];
         s[j] = e.rope_sin[pos * 128 + i];
       }
+      rr += tstride;
+      if (rr >= e.rows_per_obs) { rr -= e.rows_per_obs; ++obs; }
     }
     const float sgn = (n & 1) ? 1.f : -1.f;
     float x[NC];
@@ -185,17 +213,15 @@ __device__ __forceinline__ void gemm_epilogue_cols(const GemmEpi& e, const EpiTh
 #pragma unroll
     for (int j = 0; j < NC; ++j) {
       if (j < n_valid) {
-        const int t = t0 + j * tstride;
         const bf16 o = __float2bfloat16(x[j]);
         if (n < 2048) {
-          e.q[(size_t)t * 2048 + n] = o;
+          e.q[(size_t)(t0 + j * tstride) * 2048 + n] = o;
         } else {
-          const int obs = t / e.rows_per_obs, r = t - obs * e.rows_per_obs;
-          const size_t row = (size_t)obs * e.kv_obs_stride + e.kv_row_off + r;
+          const size_t row = (size_t)lobs[j] * e.kv_obs_stride + e.kv_row_off + lrow[j];
           if (n < 2304) e.kc[row * 256 + (n - 2048)] = o;
           else {
             e.vc[row * 256 + (n - 2304)] = o;
-            if (e.vt) e.vt[((size_t)obs * 256 + (n - 2304)) * e.vt_ld + e.kv_row_off + r] = o;
+            if (e.vt) e.vt[((size_t)lobs[j] * 256 + (n - 2304)) * e.vt_ld + e.kv_row_off + lrow[j]] = o;
           }
         }
       }
@@ -244,6 +270,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     tma_prefetch_desc(&p.tmA);
     tma_prefetch_desc(&p.tmB);
     if (DUAL) tma_prefetch_desc(&p.tmA2);
+    if (p.out_mode) tma_prefetch_desc(&p.tmOut);
   }
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
   tc_fence_before();
@@ -346,7 +373,68 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
 
   if (!SPLITK || split == 1) {
-    if (is_epi && acc_ok) {
+    if (is_epi && acc_ok && p.out_mode != 0) {
+      // Tile stores through TMA: each warp stages a 32-token x 32-feature block in shared memory (the pipeline
+      // stages are free once the accumulator is complete) and one lane hands it to the TMA unit, which also
+      // clips the rows/columns beyond the tensor.  Scattered 2- and 4-byte st.global from the thread-per-
+      // feature layout cost ~30 cycles per instruction and dominated the epilogue of the large tiles.
+      const bool f32 = p.out_mode != 1;
+      uint8_t* stg = smem + (warp - 2) * 8192;              // two 4 KB slots per warp
+      const uint32_t stg_addr = smem_base + (warp - 2) * 8192;
+      const int x0 = feat0 + q * 32;
+      int it = 0;
+      for (int c0 = 32 * half; c0 < umma_n; c0 += 64, ++it) {
+        uint32_t v[32], v2[32];
+        if (threadIdx.x == 64 && c0 == 0) GEMM_TRACE(7);
+        tmem_ld32(t_lane + c0, v);
+        if (DUAL) tmem_ld32(t_lane + BN + c0, v2);
+        tmem_ld_wait();
+        if (threadIdx.x == 64 && c0 == 0) GEMM_TRACE(8);
+        const int slot = it & 1;
+        if (it >= 2) {   // the store issued two chunks ago must have finished reading this slot
+          if (lane == 0) bulk_wait_read<1>();
+          __syncwarp();
+        }
+        float x[32];
+        if (p.epi.kind == EPI_BF16) {
+          if (p.epi.act == ACT_GEGLU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) x[j] = gelu_tanh_f(__uint_as_float(v[j]) + th.bias) * __uint_as_float(v2[j]);
+          } else if (p.epi.act == ACT_GELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) x[j] = gelu_tanh_f(__uint_as_float(v[j]) + th.bias);
+          } else if (p.epi.act == ACT_SILU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) x[j] = silu_f(__uint_as_float(v[j]) + th.bias);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(v[j]) + th.bias;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(v[j]) * th.gate + th.bias;
+        }
+        if (f32) {
+          float* d = reinterpret_cast<float*>(stg + slot * 4096) + lane;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) d[j * 32] = x[j];
+        } else {
+          bf16* d = reinterpret_cast<bf16*>(stg + slot * 4096) + lane;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) d[j * 32] = __float2bfloat16(x[j]);
+        }
+        fence_proxy_async_shared();
+        __syncwarp();
+        if (lane == 0 && x0 < p.n_feat) {
+          if (p.out_mode == 3) tma_reduce_add_2d(&p.tmOut, stg_addr + slot * 4096, x0, tok0 + c0);
+          else tma_store_2d(&p.tmOut, stg_addr + slot * 4096, x0, tok0 + c0);
+          bulk_commit();
+        }
+        if (threadIdx.x == 64 && c0 == 0) GEMM_TRACE(9);
+      }
+      if (lane == 0) bulk_wait_all();
+      __syncwarp();
+    } else if (is_epi && acc_ok) {
       for (int c0 = 32 * half; c0 < umma_n; c0 += 64) {
         uint32_t v[32], v2[32];
         tmem_ld32(t_lane + c0, v);

@@ -65,6 +65,27 @@ bool make_tmap(CUtensorMap* tm, const void* base, long long K, long long rows, l
   return true;
 }
 
+// output tile map for TMA stores: [rows, cols] row-major with pitch ld (elements), box 32 x 32, no swizzle
+bool make_out_tmap(CUtensorMap* tm, const void* base, bool f32, long long cols, long long rows, long long ld, std::string* err) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) { *err = "cuTensorMapEncodeTiled entry point not found"; return false; }
+  const int esz = f32 ? 4 : 2;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * esz};
+  cuuint32_t box[2] = {32u, 32u};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = fn(tm, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[200];
+    snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled (output) failed (%d) cols=%lld rows=%lld ld=%lld", (int)r, cols, rows, ld);
+    *err = buf;
+    return false;
+  }
+  return true;
+}
+
 // ---------------------------------------------------------------------------------------------------
 // generic launch with optional cluster dimension and programmatic dependent launch
 template <typename... KArgs, typename... Args>
@@ -191,6 +212,19 @@ bool build_gemm(GemmOp* op, const bf16* w, const bf16* w2, int n_feat, int n_fea
   op->p.n_tok = tokens;
   op->p.k_blocks = kb;
   op->p.split = split;
+  // Large-token, unsplit launches write their output tiles through TMA where the epilogue is a plain tile
+  // write: bf16 outputs, and fp32 residual outputs without row remapping or a bf16 mirror.
+  op->p.out_mode = 0;
+  if (split == 1 && tokens > 64) {
+    if (epi.kind == EPI_BF16 && (epi.ld_out * 2) % 16 == 0 && ((uintptr_t)epi.out % 16) == 0) {
+      if (!make_out_tmap(&op->p.tmOut, epi.out, false, n_feat, tokens, epi.ld_out, err)) return false;
+      op->p.out_mode = 1;
+    } else if (epi.kind == EPI_RESID && epi.out_rpo == 0 && epi.res_mod == 0 && !epi.mirror && (epi.ld_outf * 4) % 16 == 0 &&
+               ((uintptr_t)epi.outf % 16) == 0 && (epi.res_in == nullptr || (epi.res_in == epi.outf && epi.ld_res == epi.ld_outf))) {
+      if (!make_out_tmap(&op->p.tmOut, epi.outf, true, n_feat, tokens, epi.ld_outf, err)) return false;
+      op->p.out_mode = epi.res_in ? 3 : 2;
+    }
+  }
   op->p.status = status;
   op->p.epi = epi;
   op->grid = dim3(split, tok_tiles, feat_tiles);
