@@ -33,6 +33,8 @@ WORKLOADS = {
     "cfg1": dict(model="pi0", num_views=1, prompt_len=0, chunk=50, seed=0),
     "cfg2": dict(model="pi0", num_views=3, prompt_len=20, chunk=50, seed=0),
     "cfg3": dict(model="pi05", num_views=2, prompt_len=52, chunk=50, seed=1),
+    # throughput mode: 32 independent observations per forward on each GPU
+    "cfg5": dict(model="pi0", num_views=2, prompt_len=20, chunk=50, seed=0, batch=32),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
@@ -76,9 +78,10 @@ def fast_checkpoint(model, prompt_len, seed, device):
 
 def inputs(wl, device):
     g = torch.Generator(device=device).manual_seed(1234)
-    images = (torch.rand(wl["num_views"], 224, 224, 3, generator=g, device=device) * 2 - 1).to(torch.bfloat16)
-    state = torch.randn(32, generator=g, device=device).to(torch.bfloat16)
-    noise = torch.randn(wl["chunk"], 32, generator=g, device=device).to(torch.bfloat16)
+    lead = (wl["batch"],) if wl.get("batch", 1) > 1 else ()
+    images = (torch.rand(*lead, wl["num_views"], 224, 224, 3, generator=g, device=device) * 2 - 1).to(torch.bfloat16)
+    state = torch.randn(*lead, 32, generator=g, device=device).to(torch.bfloat16)
+    noise = torch.randn(*lead, wl["chunk"], 32, generator=g, device=device).to(torch.bfloat16)
     return images, state, noise
 
 
@@ -143,7 +146,7 @@ def dominant_kernel_roofline(wl, device):
     hidden[P,16384] = gelu(x Wg) * (x Wu), 4*P*2048*16384 FLOPs per launch (two P x 2048 x 16384 products), tensor-bound when P >= 512 and
     co-limited by the 134 MB weight stream at P = 256."""
     import vla_ops as gpu_ops
-    P = wl["num_views"] * 256 + wl["prompt_len"]
+    P = (wl["num_views"] * 256 + wl["prompt_len"]) * wl.get("batch", 1)      # prefix tokens per forward
     g = torch.Generator(device=device).manual_seed(7)
     x = torch.randn(P, 2048, generator=g, device=device).to(torch.bfloat16)
     wg = (torch.randn(2048, 16384, generator=g, device=device) * 0.02).to(torch.bfloat16)
@@ -175,6 +178,8 @@ def oracle_forward_fn(wl, ck):
     from oracle import vla_oracle as O
     w = {k: v.cpu() for k, v in ck.items()}
     images, state, noise = [t.cpu() for t in inputs(wl, "cpu")]
+    if wl.get("batch", 1) > 1:      # the oracle has no batch dimension: one observation of the batch per step
+        images, state, noise = images[0], state[0], noise[0]
     if wl["model"] == "pi0":
         return lambda: O.pi0_forward(w, images, state, noise)
     return lambda: O.pi05_forward(w, images, noise)
@@ -262,7 +267,7 @@ def main():
     if wl["model"] == "pi0":
         from pi0_infer import Pi0Inference
         ck = fast_checkpoint("pi0", wl["prompt_len"], wl["seed"], device)
-        infer = Pi0Inference(ck, wl["num_views"], wl["chunk"], device=local, flags=args.flags)
+        infer = Pi0Inference(ck, wl["num_views"], wl["chunk"], device=local, flags=args.flags, batch=wl.get("batch", 1))
         images, state, noise = inputs(wl, device)
         step = lambda: infer.forward(images, state, noise)
         host_args = [t.cpu().pin_memory() for t in (images, state, noise)]
@@ -336,20 +341,21 @@ def main():
     stage_ms = infer._engine.time_stages()
 
     if rank == 0:
+        obs = wl.get("batch", 1)          # observations per step and GPU
         h2d = sum(x.numel() * 2 for x in host_args)
-        d2h = wl["chunk"] * 32 * 2
-        line = {"metric": "observations_per_s", "value": round(world * args.steps / (total_ms * 1e-3), 3), "unit": "obs/s",
+        d2h = obs * wl["chunk"] * 32 * 2
+        line = {"metric": "observations_per_s", "value": round(obs * world * args.steps / (total_ms * 1e-3), 3), "unit": "obs/s",
                 "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": round(total_ms / args.steps, 4),
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": args.workload, **{k: wl[k] for k in ("model", "num_views", "prompt_len", "chunk")},
-                           "euler_steps": 10, "batch_per_gpu": 1, "parallelism": "replicas x%d" % world,
+                           "euler_steps": 10, "batch_per_gpu": obs, "parallelism": "replicas x%d" % world,
                            "l2": "5.2 GB of weights streamed per step, 40x the 126 MB L2; no flush needed"},
                 "latency_ms": {"p50": round(percentile(lat, 0.5), 4), "p99": round(percentile(lat, 0.99), 4)},
                 "stage_ms": {"vision": round(stage_ms[0], 4), "prefix": round(stage_ms[1], 4), "decoder": round(stage_ms[2], 4),
                              "note": "eager launches with events between stages, outside the graph"},
-                "e2e": {"value": round(world * args.steps / (e2e_ms * 1e-3), 3), "unit": "obs/s", "h2d_bytes_per_step": h2d,
+                "e2e": {"value": round(obs * world * args.steps / (e2e_ms * 1e-3), 3), "unit": "obs/s", "h2d_bytes_per_step": h2d,
                         "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms / args.steps, 4)},
-                "decoder_stream": decoder_stream(wl, stage_ms[2]),
+                "decoder_stream": decoder_stream(wl, stage_ms[2]) if obs == 1 else None,
                 "gpu_launches": n_kernels * args.steps, "kernels_per_step": n_kernels, "device_bytes": dev_bytes,
                 "clocks": clocks}
         del infer
