@@ -135,6 +135,15 @@ class ClockSampler:
         return out
 
 
+def max_over_ranks(dist, device, values):
+    """Element-wise maximum of per-rank timings over all ranks (the step time of a multi-GPU job is set by
+    its slowest rank); works with NCCL on GPU and gloo on CPU."""
+    t = torch.tensor(values, device=device, dtype=torch.float64)
+    if dist is not None and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.tolist()
+
+
 def percentile(xs, q):
     xs = sorted(xs)
     return xs[min(len(xs) - 1, int(round(q * (len(xs) - 1))))]
@@ -334,10 +343,7 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     assert infer._engine.status_word() == 0, "device status word raised"
 
-    t = torch.tensor([total_ms, e2e_s * 1e3], device=device, dtype=torch.float64)
-    if dist:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms = t.tolist()
+    total_ms, e2e_ms = max_over_ranks(dist, device, [total_ms, e2e_s * 1e3])
     stage_ms = infer._engine.time_stages()
 
     if rank == 0:

@@ -82,6 +82,13 @@ int vla_buffer(vla_handle h, const char* name, void** dev_ptr, size_t* bytes);
  * default stream) over the library-owned I/O buffers.  Asynchronous; the caller synchronises. */
 int vla_forward(vla_handle h, void* stream);
 
+/* Runs a subset of the forward: stage_mask is a combination of 1 = vision towers + projector into the prefix
+ * residual stream ("encoder_x", fp32 [batch*P, 2048], view v in rows 256v..256v+255), 2 = prompt rows + prefix
+ * prefill (fills the K/V cache), 4 = action expert.  Used by the multi-GPU latency mode, where each view's
+ * tower runs on its own GPU and the projected tiles are gathered into the prefill GPU's "encoder_x" between
+ * stage 1 and stage 2.  No counterpart in the reference (single GPU, one graph: pi0_infer.py:1232-1236). */
+int vla_forward_stages(vla_handle h, int stage_mask, void* stream);
+
 /* Replaces Pi0Inference.forward / Pi05Inference.forward for a caller holding HOST memory
  * (pi0_infer.py:1356-1361): copies bf16 images/state/noise in, runs, copies the bf16 (batch,chunk,32)
  * actions out and synchronises.  `state` is ignored for Pi05 (may be NULL). */

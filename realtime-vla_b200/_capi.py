@@ -58,6 +58,7 @@ EXPORTS = {
     "vla_set_prompt": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int]),
     "vla_buffer": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p), C.POINTER(C.c_size_t)]),
     "vla_forward": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "vla_forward_stages": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "vla_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "vla_status_word": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
     "vla_stats": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_size_t)]),

@@ -111,6 +111,11 @@ class Engine:
         stream = torch.cuda.current_stream(self.device).cuda_stream
         _capi.check(self.lib.vla_forward(self.handle, C.c_void_p(stream)), self.handle)
 
+    def forward_stages(self, mask):
+        """Subset of the forward: 1 = vision towers + projector, 2 = prompt + prefix prefill, 4 = action expert."""
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _capi.check(self.lib.vla_forward_stages(self.handle, int(mask), C.c_void_p(stream)), self.handle)
+
     def forward_host(self, images, state, noise, out):
         """Host-memory entry: contiguous bf16 CPU tensors in, actions written to `out` (bf16 CPU)."""
         _capi.check(self.lib.vla_forward_host(self.handle, C.c_void_p(images.data_ptr()),

@@ -143,18 +143,39 @@ int pick_split(int units, int k_blocks, int sm_count) {
   return split;
 }
 
-// Token tile and K split for a GEMM of `tokens` rows over feat_tiles x k_blocks weight tiles: small token
-// counts always fit one tile; for large ones prefer 256-token tiles unless that leaves most SMs idle, in
-// which case 128-token tiles (which can split K) are used.
+// Token tile and K split for a GEMM of `tokens` rows over feat_tiles x k_blocks weight tiles.
+// Up to 128 tokens there is one token tile and the split follows pick_split.  Above that a small cost
+// model (in SM cycles) chooses between 128- and 256-token tiles and K splits of 1, 2, 4, 8:
+//   per CTA and 64-wide K block: TMA brings 16 KB per weight tile + 128 B per token row at ~64 B/clk (the
+//   per-SM L2 read rate, measured 59-62 B/clk), the MMAs take 2*bn clk per accumulator, whichever is longer;
+//   + epilogue ~22 clk per token column and accumulator (two warps per lane quarter), + ~5000 clk for the
+//   split-K exchange; x the number of waves over the SMs.
 void pick_tiling(int tokens, int feat_tiles, int k_blocks, bool dual, int sm_count, int* bn, int* split) {
-  if (tokens <= 64) *bn = 64;
-  else if (tokens <= 128) *bn = 128;
-  else {
-    const int units256 = feat_tiles * ((tokens + 255) / 256);
-    *bn = (dual || units256 * 3 >= sm_count * 2) ? 256 : 128;
+  if (tokens <= 128) {
+    *bn = tokens <= 64 ? 64 : 128;
+    *split = pick_split(feat_tiles, k_blocks, sm_count);
+    return;
   }
-  const int units = feat_tiles * ((tokens + *bn - 1) / *bn);
-  *split = can_split(*bn, dual) ? pick_split(units, k_blocks, sm_count) : 1;
+  const int accs = dual ? 2 : 1;
+  double best = 1e30;
+  *bn = 256;
+  *split = 1;
+  for (int b = 128; b <= 256; b *= 2) {
+    for (int s = 1; s <= 8; s *= 2) {
+      if (s > 1 && (k_blocks / s < 8)) continue;          // keep K slices long enough to amortise the exchange
+      const int tok_tiles = (tokens + b - 1) / b;
+      const long long ctas = (long long)feat_tiles * tok_tiles * s;
+      if (s > 1 && (size_t)ctas * 128 * b * accs > ((size_t)16 << 20)) continue;   // split-K scratch capacity (floats)
+      const int kb = (k_blocks + s - 1) / s;
+      const double load = kb * (16384.0 * accs + 128.0 * b) / 64.0;
+      const double mma = kb * 2.0 * b * accs;
+      const double epi = 22.0 * (b / 2) * accs;
+      const double cta = (load > mma ? load : mma) + epi + (s > 1 ? 5000.0 : 0.0);
+      const double waves = (double)((ctas + sm_count - 1) / sm_count);
+      const double cost = waves * cta;
+      if (cost < best) { best = cost; *bn = b; *split = s; }
+    }
+  }
 }
 
 template <int BN, bool DUAL, bool SPLITK>
@@ -369,6 +390,7 @@ struct vla_model {
   int n_kernels = 0;
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t graph_exec = nullptr;
+  std::map<int, cudaGraphExec_t> stage_graphs;   // graphs of stage subsets, captured on first use
   cudaStream_t own_stream = nullptr;
 
   int fail(int code, const char* fmt, ...) {
@@ -656,6 +678,7 @@ void plan_vision(Plan& pl) {
   e.kind = EPI_RESID; e.bias = pl.vec("encoder_multi_modal_projector_b"); e.outf = m->encoder_x; e.ld_outf = 2048;
   e.out_rpo = m->nv * 256; e.out_obs_stride = m->P;
   pl.gemm("encoder_multi_modal_projector_w", nullptr, 0, m->vision_xn, Nv, 1152, 1152, e);
+  pl.stage = 1;   // the prompt rows belong to the prefix stage (in multi-GPU latency mode the towers run elsewhere)
   if (m->L > 0) {  // pi0_infer.py:1344
     const bf16* emb = m->lang; float* x = m->encoder_x;
     const int L = m->L, P = m->P, off = m->nv * 256, B = m->B;
@@ -1049,6 +1072,37 @@ int vla_forward(vla_handle m, void* stream) {
   return run_ops(m, st);
 }
 
+int vla_forward_stages(vla_handle m, int stage_mask, void* stream) {
+  if (!m || !m->finalized) return m ? m->fail(VLA_ERR_STATE, "forward before finalize") : VLA_ERR_STATE;
+  if (stage_mask <= 0 || stage_mask > 7) return m->fail(VLA_ERR_SHAPE, "stage mask must be a combination of 1 (vision), 2 (prefix), 4 (action expert)");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  cudaSetDevice(m->cfg.device);
+  if (stage_mask == 7) return vla_forward(m, stream);
+  if (!m->use_graph) {
+    for (int sidx = 0; sidx < 3; ++sidx)
+      if (stage_mask & (1 << sidx)) { int rc = run_ops(m, st, sidx); if (rc) return rc; }
+    return VLA_OK;
+  }
+  auto it = m->stage_graphs.find(stage_mask);
+  if (it == m->stage_graphs.end()) {
+    cudaGraph_t g = nullptr;
+    CK(cudaStreamSynchronize(m->own_stream));
+    CK(cudaStreamBeginCapture(m->own_stream, cudaStreamCaptureModeThreadLocal));
+    int rc = VLA_OK;
+    for (int sidx = 0; sidx < 3 && !rc; ++sidx)
+      if (stage_mask & (1 << sidx)) rc = run_ops(m, m->own_stream, sidx);
+    cudaError_t ce = cudaStreamEndCapture(m->own_stream, &g);
+    if (rc) return rc;
+    if (ce != cudaSuccess) return m->fail(VLA_ERR_CUDA, "stage graph capture failed: %s", cudaGetErrorString(ce));
+    cudaGraphExec_t ge = nullptr;
+    CK(cudaGraphInstantiate(&ge, g, 0));
+    cudaGraphDestroy(g);
+    it = m->stage_graphs.emplace(stage_mask, ge).first;
+  }
+  CK(cudaGraphLaunch(it->second, st));
+  return VLA_OK;
+}
+
 int vla_forward_host(vla_handle m, const void* images, const void* state, const void* noise, void* actions_out) {
   if (!m || !m->finalized) return m ? m->fail(VLA_ERR_STATE, "forward before finalize") : VLA_ERR_STATE;
   if (!images || !noise || !actions_out || (!m->pi05 && !state)) return m->fail(VLA_ERR_STATE, "null input");
@@ -1102,6 +1156,7 @@ int vla_destroy(vla_handle m) {
   cudaSetDevice(m->cfg.device);
   cudaDeviceSynchronize();
   if (m->graph_exec) cudaGraphExecDestroy(m->graph_exec);
+  for (auto& kv : m->stage_graphs) cudaGraphExecDestroy(kv.second);
   if (m->graph) cudaGraphDestroy(m->graph);
   if (m->own_stream) cudaStreamDestroy(m->own_stream);
   for (void* p : m->allocs) cudaFree(p);
