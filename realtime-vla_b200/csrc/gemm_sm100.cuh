@@ -38,6 +38,13 @@ struct GemmEpi {
   int ld_mirror;
   int out_rpo;         // > 0: token t is written to row (t / out_rpo) * out_obs_stride + t % out_rpo
   int out_obs_stride;
+  // RMS norm folded into the GEMMs around a residual stream (the normalisation has no learned scale, so
+  // norm(x) @ W = f * (x @ W) with f = rsqrt(mean(x^2) + 1e-6) per token, pi0_infer.py:1005):
+  float* ssq_out;      // EPI_RESID producer: sum of squares of the written values per (32-feature slot, token)
+  int ssq_ld;          //   ssq_out[slot * ssq_ld + token]
+  const float* ssq_in; // consumer (any kind): accumulators are scaled by f[token] from these partial sums
+  int ssq_slots;       //   number of slots (= features of the normalised stream / 32)
+  float ssq_inv_d;     //   1 / features
   // EPI_QKV: features [0,2048) = 8 query heads, [2048,2304) = key, [2304,2560) = value (head dim 256).
   // Rotary embedding on adjacent pairs of Q and K; Q -> q[t*2048 + n]; K,V -> cache rows.
   bf16* q;
@@ -97,7 +104,7 @@ struct GemmCfg {
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : (STAGES_RAW < 1 ? 1 : STAGES_RAW);
   static constexpr bool VALID = STAGES_RAW >= 3;
   static constexpr int TMEM_COLS = DUAL ? 2 * BN : BN;
-  static constexpr int BAR_BYTES = 256;
+  static constexpr int BAR_BYTES = 256 + 1024;   // barriers + TMEM slot, then per-token row scales [256]
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + RECV_BYTES + BAR_BYTES + 1024;
 };
 
@@ -151,7 +158,6 @@ __device__ __forceinline__ void gemm_epilogue_cols(const GemmEpi& e, const EpiTh
       if (j < n_valid) o[j * step] = __float2bfloat16(x[j]);
 #endif
   } else if (e.kind == EPI_RESID) {
-    if (!th.n_ok) return;
     // Row bookkeeping without per-column integer division (an emulated division per column made this epilogue
     // 3x slower than its memory traffic): one division for the first column, then incremental wrap-around.
     float r[NC];
@@ -163,7 +169,7 @@ __device__ __forceinline__ void gemm_epilogue_cols(const GemmEpi& e, const EpiTh
     for (int j = 0; j < NC; ++j) {
       orow[j] = e.out_rpo > 0 ? (size_t)o_obs * e.out_obs_stride + o_r : (size_t)(t0 + j * tstride);
       r[j] = 0.f;
-      if (j < n_valid && e.res_in) r[j] = e.res_in[(e.res_mod > 0 ? (size_t)m_r : orow[j]) * e.ld_res + n];
+      if (j < n_valid && th.n_ok && e.res_in) r[j] = e.res_in[(e.res_mod > 0 ? (size_t)m_r : orow[j]) * e.ld_res + n];
       if (e.out_rpo > 0) {
         o_r += tstride;
         if (o_r >= e.out_rpo) { o_r -= e.out_rpo; ++o_obs; }
@@ -177,9 +183,18 @@ __device__ __forceinline__ void gemm_epilogue_cols(const GemmEpi& e, const EpiTh
     for (int j = 0; j < NC; ++j) r[j] += v[j] * th.gate + th.bias;
 #pragma unroll
     for (int j = 0; j < NC; ++j) {
-      if (j < n_valid) {
+      if (j < n_valid && th.n_ok) {
         e.outf[orow[j] * e.ld_outf + n] = r[j];
         if (e.mirror) e.mirror[orow[j] * e.ld_mirror + n] = __float2bfloat16(r[j]);
+      }
+    }
+    if (e.ssq_out) {   // per-token sum of squares over this warp's 32 features (warp-collective: no early exit above)
+#pragma unroll
+      for (int j = 0; j < NC; ++j) {
+        float sq = (j < n_valid && th.n_ok) ? r[j] * r[j] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if ((threadIdx.x & 31) == 0 && j < n_valid) e.ssq_out[(size_t)(n >> 5) * e.ssq_ld + orow[j]] = sq;
       }
     }
   } else {  // EPI_QKV
@@ -352,6 +367,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
 
   // ---------------- epilogue ----------------
   const bool is_epi = warp >= 2;
+  float* row_scale = reinterpret_cast<float*>(smem + PIPE_BYTES + 256);   // [BN] when the RMS norm is folded in
+  const bool scaled = p.epi.ssq_in != nullptr;
+  if (is_epi && scaled) {
+    // 256 epilogue threads, one token each: f = rsqrt(mean(x^2) + eps) from the producer's partial sums
+    const int tt = threadIdx.x - 64;
+    if (tt < umma_n) {
+      const int t = min(tok0 + tt, p.n_tok - 1);
+      float acc = 0.f;
+      for (int sl = 0; sl < p.epi.ssq_slots; ++sl) acc += p.epi.ssq_in[(size_t)sl * p.epi.ssq_ld + t];
+      row_scale[tt] = rsqrtf(acc * p.epi.ssq_inv_d + 1e-6f);
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight epilogue warps
+  }
   const int q = warp & 3;                 // TMEM lane quarter this warp may read
   const int half = (warp - 2) >> 2;       // the two warps of a quarter take alternate column chunks
   const int fl = q * 32 + lane;           // feature lane 0..127
@@ -390,6 +418,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         if (DUAL) tmem_ld32(t_lane + BN + c0, v2);
         tmem_ld_wait();
         if (threadIdx.x == 64 && c0 == 0) GEMM_TRACE(8);
+        if (scaled) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = __float_as_uint(__uint_as_float(v[j]) * row_scale[c0 + j]);
+            if (DUAL) v2[j] = __float_as_uint(__uint_as_float(v2[j]) * row_scale[c0 + j]);
+          }
+        }
         const int slot = it & 1;
         if (it >= 2) {   // the store issued two chunks ago must have finished reading this slot
           if (lane == 0) bulk_wait_read<1>();
@@ -440,6 +475,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         tmem_ld32(t_lane + c0, v);
         if (DUAL) tmem_ld32(t_lane + BN + c0, v2);
         tmem_ld_wait();
+        if (scaled) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = __float_as_uint(__uint_as_float(v[j]) * row_scale[c0 + j]);
+            if (DUAL) v2[j] = __float_as_uint(__uint_as_float(v2[j]) * row_scale[c0 + j]);
+          }
+        }
         const int n_valid = min(32, p.n_tok - (tok0 + c0));
         gemm_epilogue_cols<32>(p.epi, th, tok0 + c0, 1, n_valid, reinterpret_cast<const float*>(v),
                                reinterpret_cast<const float*>(v2));
@@ -490,6 +532,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           }
           s1[ci] = ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
           s2[ci] = ((b[0] + b[1]) + (b[2] + b[3])) + ((b[4] + b[5]) + (b[6] + b[7]));
+          if (scaled) {
+            const float f = row_scale[min(c, BN - 1)];
+            s1[ci] *= f;
+            s2[ci] *= f;
+          }
         }
         const int n_valid = min(4, n_owned - i0);
         gemm_epilogue_cols<4>(p.epi, th, tok0 + rank + i0 * split, split, n_valid, s1, s2);

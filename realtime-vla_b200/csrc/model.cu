@@ -136,10 +136,8 @@ size_t gemm_scratch_floats(int bn, bool dual, dim3 grid) {
 
 int pick_split(int units, int k_blocks, int sm_count) {
   int split = 1;
-  // Split only up to about half of the SMs: consecutive kernels overlap through programmatic dependent
-  // launch (the next kernel prefetches its weights on the SMs this one leaves free), and clusters of 8 fit
-  // only ~16 at a time on the 8 GPCs anyway.
-  while (split < 8 && units * split * 2 <= (sm_count * 9) / 16 && split * 2 <= k_blocks) split *= 2;
+  // Split while all CTAs still fit the SMs in one wave (clusters of 8 fit ~16 at a time on the 8 GPCs).
+  while (split < 8 && units * split * 2 <= sm_count && split * 2 <= k_blocks) split *= 2;
   return split;
 }
 
@@ -374,6 +372,8 @@ struct vla_model {
   bf16 *kcache, *vcache, *vtcache;
   int T_pad;
   float *decoder_x, *state_tok;
+  bf16* decoder_xb;      // bf16 copy of the un-normalised suffix stream (operand of the GEMMs with folded RMS norm)
+  float* decoder_ssq;    // [32 slots][suffix tokens] partial sums of squares of that stream
   bf16 *decoder_xn, *decoder_q, *decoder_attn, *decoder_hidden, *decoder_act, *decoder_xfin;
   bf16* lang;
   float *rope_cos, *rope_sin;
@@ -532,6 +532,8 @@ bool alloc_buffers(vla_model* m) {
   ok &= m->dalloc(&m->decoder_x, Ns * 1024, "decoder_x");
   ok &= m->dalloc(&m->state_tok, B * 1024);
   ok &= m->dalloc(&m->decoder_xn, Ns * 1024);
+  ok &= m->dalloc(&m->decoder_xb, Ns * 1024);
+  ok &= m->dalloc(&m->decoder_ssq, (size_t)32 * Ns);
   ok &= m->dalloc(&m->decoder_q, Ns * 2048);
   ok &= m->dalloc(&m->decoder_attn, Ns * 2048);
   ok &= m->dalloc(&m->decoder_hidden, Ns * 4096);
@@ -766,13 +768,18 @@ void plan_decoder(Plan& pl) {
       bf16* vt = m->vtcache + (size_t)l * B * 256 * m->T_pad;
       const float* st_attn = pi05 ? m->style_attn + ((size_t)step * m->nl + l) * 3072 : nullptr;
       const float* st_ffn = pi05 ? m->style_ffn + ((size_t)step * m->nl + l) * 3072 : nullptr;
-      pl.norm(m->decoder_x, m->decoder_xn, Ns, 1024, pi05 ? NORM_ADARMS : NORM_RMS, st_attn, nullptr);
+      // Pi0: the scale-free RMS norms are folded into the GEMMs (f * (x @ W)); only the first layer of a step
+      // normalises explicitly, because its input comes from the action MLP.  Pi05 (adaRMS) keeps the norm kernels.
+      const bool fold = !pi05;
+      const bool explicit_norm = !fold || l == 0;
+      if (explicit_norm) pl.norm(m->decoder_x, m->decoder_xn, Ns, 1024, pi05 ? NORM_ADARMS : NORM_RMS, st_attn, nullptr);
       GemmEpi e = pl.epi0();
       e.kind = EPI_QKV; e.q = m->decoder_q; e.kc = kc; e.vc = vc; e.rope_cos = m->rope_cos; e.rope_sin = m->rope_sin;
       e.pos_off = pi05 ? 0 : m->P; e.pos_base = pi05 ? m->d_pos_base : nullptr;
       e.rows_per_obs = S; e.kv_obs_stride = m->T; e.kv_row_off = m->P;
       e.vt = vt; e.vt_ld = m->T_pad;
-      pl.gemm("decoder_attn_qkv_w", nullptr, l, m->decoder_xn, Ns, 1024, 1024, e);
+      if (!explicit_norm) { e.ssq_in = m->decoder_ssq; e.ssq_ld = Ns; e.ssq_slots = 32; e.ssq_inv_d = 1.0f / 1024.0f; }
+      pl.gemm("decoder_attn_qkv_w", nullptr, l, explicit_norm ? m->decoder_xn : m->decoder_xb, Ns, 1024, 1024, e);
       AttnParams a; memset(&a, 0, sizeof a);
       a.q = m->decoder_q; a.k = kc; a.v = vc; a.o = m->decoder_attn;
       a.ldq = a.ldk = a.ldv = a.ldo = 256;
@@ -786,14 +793,17 @@ void plan_decoder(Plan& pl) {
       e = pl.epi0();
       e.kind = EPI_RESID; e.outf = m->decoder_x; e.ld_outf = 1024; e.res_in = m->decoder_x; e.ld_res = 1024;
       e.gate = pi05 ? st_attn + 2048 : nullptr;
+      if (fold) { e.mirror = m->decoder_xb; e.ld_mirror = 1024; e.ssq_out = m->decoder_ssq; e.ssq_ld = Ns; }
       pl.gemm("decoder_attn_o_w", nullptr, l, m->decoder_attn, Ns, 2048, 2048, e);
-      pl.norm(m->decoder_x, m->decoder_xn, Ns, 1024, pi05 ? NORM_ADARMS : NORM_RMS, st_ffn, nullptr);
+      if (!fold) pl.norm(m->decoder_x, m->decoder_xn, Ns, 1024, NORM_ADARMS, st_ffn, nullptr);
       e = pl.epi0();
       e.kind = EPI_BF16; e.act = ACT_GEGLU; e.out = m->decoder_hidden; e.ld_out = 4096;
-      pl.gemm("decoder_ffn_gate_w", "decoder_ffn_up_w", l, m->decoder_xn, Ns, 1024, 1024, e);
+      if (fold) { e.ssq_in = m->decoder_ssq; e.ssq_ld = Ns; e.ssq_slots = 32; e.ssq_inv_d = 1.0f / 1024.0f; }
+      pl.gemm("decoder_ffn_gate_w", "decoder_ffn_up_w", l, fold ? m->decoder_xb : m->decoder_xn, Ns, 1024, 1024, e);
       e = pl.epi0();
       e.kind = EPI_RESID; e.outf = m->decoder_x; e.ld_outf = 1024; e.res_in = m->decoder_x; e.ld_res = 1024;
       e.gate = pi05 ? st_ffn + 2048 : nullptr;
+      if (fold) { e.mirror = m->decoder_xb; e.ld_mirror = 1024; e.ssq_out = m->decoder_ssq; e.ssq_ld = Ns; }
       pl.gemm("decoder_ffn_down_w", nullptr, l, m->decoder_hidden, Ns, 4096, 4096, e);
     }
     // Euler update: noise += norm(x_action) @ W_out + b_out   (pi0_infer.py:1224-1230, pi05_infer.py:511-523)
