@@ -40,7 +40,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from the ncu
 # capture summarised under profiles/), keyed by workload; None until a capture exists.
-NCU_TRAFFIC_BYTES = {"cfg2": None, "cfg1": None, "cfg3": None}
+NCU_TRAFFIC_BYTES = {"cfg2": 144486144, "cfg1": None, "cfg3": None, "cfg5": None}   # profiles/gemm_sm100_geglu_prefix_p788.md
 
 
 def peaks():
@@ -170,6 +170,40 @@ def dominant_kernel_roofline(wl, device):
             "traffic": None}
 
 
+def expert_down_roofline(wl, device):
+    """Action-expert down projection x[S,1024] += hidden[S,4096] @ Wd: 8.4 MB of weights per launch, split over a
+    cluster of 8 along K; HBM-bound (the weights are read exactly once per launch)."""
+    import vla_ops
+    S = wl["chunk"] + (1 if wl["model"] == "pi0" else 0)
+    g = torch.Generator(device=device).manual_seed(7)
+    x = torch.randn(S, 4096, generator=g, device=device).to(torch.bfloat16)
+    w = (torch.randn(4096, 1024, generator=g, device=device) * 0.02).to(torch.bfloat16)
+    res = torch.randn(S, 1024, generator=g, device=device)
+    _, ms = vla_ops.gemm(x, w, epi=1, res=res, iters=50)
+    nbytes = 4096 * 1024 * 2 + S * 4096 * 2 + 2 * S * 1024 * 4
+    pk, which = peaks()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"kernel": "gemm_sm100_kernel<64,single,split 8> expert down projection S=%d" % S, "bound": "hbm", "achieved": round(gbs, 1),
+            "peak": pk["hbm_gbs"], "peak_source": which, "unit": "GB/s", "frac": round(gbs / pk["hbm_gbs"], 4),
+            "ms_per_launch": round(ms, 5), "bytes_per_launch": nbytes,
+            "note": "back-to-back launches of one shape: the 8.4 MB of weights stay in L2, so this is the launch-latency floor, not a DRAM figure"}
+
+
+def expert_attention_timing(wl, device):
+    """Suffix attention of one action-expert layer: 8 S query rows over P + S keys, head dim 256, Pi0 mask."""
+    import vla_ops
+    P = wl["num_views"] * 256 + wl["prompt_len"]
+    S = wl["chunk"] + (1 if wl["model"] == "pi0" else 0)
+    g = torch.Generator(device=device).manual_seed(7)
+    q = torch.randn(S * 8, 256, generator=g, device=device).to(torch.bfloat16)
+    k = torch.randn(P + S, 256, generator=g, device=device).to(torch.bfloat16)
+    v = torch.randn(P + S, 256, generator=g, device=device).to(torch.bfloat16)
+    _, ms = vla_ops.attention_tc(q, k, v, prefix_alloc=P, valid_prefix=P, restrict_rows=8, scale=1 / 16, iters=50)
+    flops = 4.0 * S * 8 * (P + S) * 256
+    return {"kernel": "attention_tc_kernel suffix attention rows=%d keys=%d" % (S * 8, P + S), "bound": "latency",
+            "achieved": round(flops / (ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s", "ms_per_launch": round(ms, 5)}
+
+
 def decoder_stream(wl, decoder_ms):
     """Action-expert weight streaming: algorithmic bytes of the 10 Euler steps (18 layers x 34.603 MB of weights
     + 2.23 MB of in/out projections + the K/V cache rows read by the suffix attention, per step) over the
@@ -245,8 +279,10 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--flags", type=int, default=0, help="vla_config.flags: 1 = no programmatic dependent launch, 2 = no CUDA graph")
-    ap.add_argument("--microbench", action="store_true",
-                    help="time only the dominant kernel of the workload (prefix GeGLU GEMM) and print its roofline object")
+    ap.add_argument("--microbench", nargs="?", const="geglu", default=None, choices=["geglu", "expert_down", "expert_attention"],
+                    help="time one kernel alone and print its roofline object: geglu = the dominant kernel of the workload "
+                         "(prefix GeGLU GEMM); expert_down = action-expert down projection (51 x 4096 -> 1024, HBM-bound weight "
+                         "stream); expert_attention = suffix attention of the action expert on the tcgen05 kernel")
     ap.add_argument("--profile-forward", action="store_true",
                     help="run two forwards and bracket the second with cudaProfilerStart/Stop (for ncu "
                          "--profile-from-start off); prints no benchmark line")
@@ -265,7 +301,8 @@ def main():
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if args.microbench:
-        print(json.dumps(dominant_kernel_roofline(wl, device)), flush=True)
+        fn = {"geglu": dominant_kernel_roofline, "expert_down": expert_down_roofline, "expert_attention": expert_attention_timing}
+        print(json.dumps(fn[args.microbench](wl, device)), flush=True)
         return
     dist = None
     if world > 1:
