@@ -76,9 +76,12 @@ struct GemmParams {
   CUtensorMap tmA;   // weights [features_padded, Kp], box 64 x 128
   CUtensorMap tmA2;  // second weight (GeGLU "up"), only for DUAL
   CUtensorMap tmB;   // activations [tokens, K], box 64 x BN
-  CUtensorMap tmOut; // output [tokens, features], box 32 x 32, no swizzle (see out_mode)
+  CUtensorMap tmOut; // output [tokens, features], box 32 x 32, no swizzle (see out_mode); QKV: the query buffer
+  CUtensorMap tmOut2; // QKV only: key cache rows [kv_row_off + tokens, 256]
+  CUtensorMap tmOut3; // QKV only: value cache rows
   int out_mode;      // 0: epilogue stores with plain st.global; 1: bf16 tile stores through TMA; 2: fp32 tile stores;
-                     // 3: fp32 tile reduce-add (in-place residual: x += gate*acc + bias, one add per element)
+                     // 3: fp32 tile reduce-add (in-place residual: x += gate*acc + bias, one add per element);
+                     // 4: QKV with rotary embedding, bf16 tile stores into the query buffer and the K/V cache
   int n_feat;        // valid features
   int n_tok;         // valid tokens
   int k_blocks;      // Kp / 64
@@ -111,6 +114,11 @@ struct GemmCfg {
 // smem matrix descriptor: K-major tile, rows of 128 B, 128-byte swizzle, 8-row groups 1024 B apart.
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
   return (uint64_t)((smem_addr & 0x3FFFF) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
 }
 
 // Per-thread epilogue constants (this thread owns feature n for every token column of the tile).
@@ -286,6 +294,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     tma_prefetch_desc(&p.tmB);
     if (DUAL) tma_prefetch_desc(&p.tmA2);
     if (p.out_mode) tma_prefetch_desc(&p.tmOut);
+    if (p.out_mode == 4) { tma_prefetch_desc(&p.tmOut2); tma_prefetch_desc(&p.tmOut3); }
   }
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
   tc_fence_before();
@@ -406,7 +415,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       // stages are free once the accumulator is complete) and one lane hands it to the TMA unit, which also
       // clips the rows/columns beyond the tensor.  Scattered 2- and 4-byte st.global from the thread-per-
       // feature layout cost ~30 cycles per instruction and dominated the epilogue of the large tiles.
-      const bool f32 = p.out_mode != 1;
+      const bool f32 = p.out_mode == 2 || p.out_mode == 3;
       uint8_t* stg = smem + (warp - 2) * 8192;              // two 4 KB slots per warp
       const uint32_t stg_addr = smem_base + (warp - 2) * 8192;
       const int x0 = feat0 + q * 32;
@@ -445,6 +454,39 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
 #pragma unroll
             for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(v[j]) + th.bias;
           }
+        } else if (p.epi.kind == EPI_QKV) {
+          // rotary embedding on adjacent feature pairs (lanes 2i, 2i+1) of Q and K; single observation: row = token
+          const bool rot = n < 2304;
+          const int fi = (n & 255) >> 1;
+          const float sgn = (n & 1) ? 1.f : -1.f;
+          float cs[32], sn[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int pos = min(tok0 + c0 + j, p.n_tok - 1) + p.epi.pos_off + th.pos_base;
+            cs[j] = rot ? p.epi.rope_cos[pos * 128 + fi] : 1.f;
+            sn[j] = rot ? p.epi.rope_sin[pos * 128 + fi] : 0.f;
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float val = __uint_as_float(v[j]);
+            const float partner = __shfl_xor_sync(0xffffffffu, val, 1);
+            x[j] = val * cs[j] + sgn * partner * sn[j];
+          }
+          if (n >= 2304 && p.epi.vt) {   // transposed value cache: this thread owns row d, 32 consecutive keys
+            bf16* dst = p.epi.vt + (size_t)(n - 2304) * p.epi.vt_ld + p.epi.kv_row_off + tok0 + c0;
+            const bool vec = (((size_t)(p.epi.kv_row_off + tok0 + c0) | (size_t)p.epi.vt_ld) & 7) == 0 && tok0 + c0 + 32 <= p.n_tok;
+            if (vec) {
+#pragma unroll
+              for (int g = 0; g < 4; ++g)
+                *reinterpret_cast<uint4*>(dst + 8 * g) =
+                    make_uint4(pack2_bf16(x[8 * g], x[8 * g + 1]), pack2_bf16(x[8 * g + 2], x[8 * g + 3]),
+                               pack2_bf16(x[8 * g + 4], x[8 * g + 5]), pack2_bf16(x[8 * g + 6], x[8 * g + 7]));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (tok0 + c0 + j < p.n_tok) dst[j] = __float2bfloat16(x[j]);
+            }
+          }
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(v[j]) * th.gate + th.bias;
@@ -462,6 +504,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         __syncwarp();
         if (lane == 0 && x0 < p.n_feat) {
           if (p.out_mode == 3) tma_reduce_add_2d(&p.tmOut, stg_addr + slot * 4096, x0, tok0 + c0);
+          else if (p.out_mode == 4 && x0 >= 2304) tma_store_2d(&p.tmOut3, stg_addr + slot * 4096, x0 - 2304, p.epi.kv_row_off + tok0 + c0);
+          else if (p.out_mode == 4 && x0 >= 2048) tma_store_2d(&p.tmOut2, stg_addr + slot * 4096, x0 - 2048, p.epi.kv_row_off + tok0 + c0);
           else tma_store_2d(&p.tmOut, stg_addr + slot * 4096, x0, tok0 + c0);
           bulk_commit();
         }

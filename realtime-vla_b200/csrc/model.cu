@@ -158,7 +158,10 @@ void pick_tiling(int tokens, int feat_tiles, int k_blocks, bool dual, int sm_cou
   double best = 1e30;
   *bn = 256;
   *split = 1;
-  for (int b = 128; b <= 256; b *= 2) {
+  // up to 256 tokens a 128-token tile always measured at least as fast as one 256-token tile (more CTAs, a
+  // cheaper split-K exchange); dual-accumulator GEMMs keep 256 (their main loop is MMA-bound only there)
+  const int b_max = (tokens <= 256 && !dual) ? 128 : 256;
+  for (int b = 128; b <= b_max; b *= 2) {
     for (int s = 1; s <= 8; s *= 2) {
       if (s > 1 && (k_blocks / s < 8)) continue;          // keep K slices long enough to amortise the exchange
       const int tok_tiles = (tokens + b - 1) / b;
@@ -168,8 +171,10 @@ void pick_tiling(int tokens, int feat_tiles, int k_blocks, bool dual, int sm_cou
       const double load = kb * (16384.0 * accs + 128.0 * b) / 64.0;
       const double mma = kb * 2.0 * b * accs;
       const double epi = 22.0 * (b / 2) * accs;
-      const double cta = (load > mma ? load : mma) + epi + (s > 1 ? 5000.0 : 0.0);
-      const double waves = (double)((ctas + sm_count - 1) / sm_count);
+      const double exch = s > 1 ? 5000.0 * (b / 128) * accs : 0.0;     // partial tile through L2 + cluster barrier
+      const double cta = (load > mma ? load : mma) + epi + exch;
+      const int resident = s == 8 ? 128 : (s == 4 ? 144 : sm_count);  // clusters are scheduled whole within a GPC
+      const double waves = (double)((ctas + resident - 1) / resident);
       const double cost = waves * cta;
       if (cost < best) { best = cost; *bn = b; *split = s; }
     }
@@ -242,6 +247,11 @@ bool build_gemm(GemmOp* op, const bf16* w, const bf16* w2, int n_feat, int n_fea
                ((uintptr_t)epi.outf % 16) == 0 && (epi.res_in == nullptr || (epi.res_in == epi.outf && epi.ld_res == epi.ld_outf))) {
       if (!make_out_tmap(&op->p.tmOut, epi.outf, true, n_feat, tokens, epi.ld_outf, err)) return false;
       op->p.out_mode = epi.res_in ? 3 : 2;
+    } else if (epi.kind == EPI_QKV && epi.rows_per_obs >= tokens) {
+      if (!make_out_tmap(&op->p.tmOut, epi.q, false, 2048, tokens, 2048, err)) return false;
+      if (!make_out_tmap(&op->p.tmOut2, epi.kc, false, 256, epi.kv_row_off + tokens, 256, err)) return false;
+      if (!make_out_tmap(&op->p.tmOut3, epi.vc, false, 256, epi.kv_row_off + tokens, 256, err)) return false;
+      op->p.out_mode = 4;
     }
   }
   op->p.status = status;

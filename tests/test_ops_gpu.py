@@ -190,7 +190,7 @@ def test_gemm_patch_embed_position_rows():
     assert_close(out, x.float() @ w.float() + pos.repeat(2, 1), rel=1e-4, what="patch embed")
 
 
-@pytest.mark.parametrize("tokens,K,pos_off,split", [(51, 1024, 788, 4), (788, 2048, 0, 1), (256, 2048, 0, 4)])
+@pytest.mark.parametrize("tokens,K,pos_off,split", [(51, 1024, 788, 4), (788, 2048, 0, 1), (256, 2048, 0, 4), (300, 1024, 100, 1), (200, 1024, 64, 1)])
 def test_gemm_qkv_rope(tokens, K, pos_off, split):
     import vla_ops as gpu_ops
     d = dev()
