@@ -17,6 +17,7 @@
 //
 // Visibility of key j for query row i: see attention.cuh (same rule, same parameters).
 #pragma once
+#include <type_traits>
 #include "common.cuh"
 
 struct AttnTcParams {
@@ -75,6 +76,8 @@ __device__ __forceinline__ float ex2_approx(float x) {
 __device__ __forceinline__ void named_barrier_sync(int id, int n_threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n_threads) : "memory");
 }
+
+__device__ __forceinline__ uint64_t low_bits64(int n) { return n >= 64 ? ~0ull : ((1ull << n) - 1ull); }
 
 __global__ void __launch_bounds__(AttnTcCfg::THREADS, 1) attention_tc_kernel(const __grid_constant__ AttnTcParams p) {
   using C = AttnTcCfg;
@@ -188,6 +191,7 @@ __global__ void __launch_bounds__(AttnTcCfg::THREADS, 1) attention_tc_kernel(con
   const int i = row0 + r;                 // global query row
   const uint32_t lane_off = (uint32_t)(q * 32) << 16;
   float m_run = -1e30f, l_run = 0.f;      // l_run: sum over this thread's keys only
+  const bool warp_live = row0 + q * 32 < p.n_q;   // warp-uniform: false when all 32 rows lie beyond n_q
   bool ok = true;
   if (is_sm) {
     const int valid_prefix = p.valid_prefix_ptr ? min(max(*p.valid_prefix_ptr, 0), p.prefix_alloc) : p.valid_prefix;
@@ -203,23 +207,40 @@ __global__ void __launch_bounds__(AttnTcCfg::THREADS, 1) attention_tc_kernel(con
       tc_fence_after();
       KTRACE_B(25, 64, p.ksplit - 1);
       const int key0 = (ch_begin + c) * 128 + half * 64;
+      // Visibility of this thread's 64 keys as a bit mask.  Most chunks are entirely visible; the one or two
+      // that straddle the prefix/suffix boundaries test one bit per key; a half chunk without a visible key
+      // (beyond the last key, or a warp whose 32 rows all lie beyond n_q) only clears its half of P.  The
+      // mode is warp-uniform because the TMEM loads below are warp-collective.
+      uint64_t vmask;
+      {
+        const int n1 = min(max(lim1 - key0, 0), 64);
+        const int a2 = min(max(lo2 - key0, 0), 64), b2 = min(max(hi2 + 1 - key0, 0), 64);
+        vmask = low_bits64(n1) | (b2 > a2 ? (low_bits64(b2) & ~low_bits64(a2)) : 0ull);
+        if (!warp_live) vmask = 0ull;
+      }
+      const bool all_vis = __all_sync(0xffffffffu, vmask == ~0ull);
+      const bool none_vis = __all_sync(0xffffffffu, vmask == 0ull);
       // pass 1: masked, scaled logits of this thread's 64 keys -> maximum
       float m_loc = -1e30f;
-      if (ok) {
+      if (ok && !none_vis) {
 #pragma unroll
         for (int c0 = 0; c0 < 64; c0 += 32) {
           uint32_t v[32];
           tmem_ld32(tmem_S + lane_off + half * 64 + c0, v);
           tmem_ld_wait();
-          float mx[4] = {-1e30f, -1e30f, -1e30f, -1e30f};
+          float mx[4] = {-3.0e38f, -3.0e38f, -3.0e38f, -3.0e38f};
+          if (all_vis) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int key = key0 + c0 + j;
-            const bool vis = (key < lim1) | ((key >= lo2) & (key <= hi2));
-            mx[j & 3] = fmaxf(mx[j & 3], vis ? __uint_as_float(v[j]) * p.scale_log2e : -1e30f);
+            for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(v[j]));
+          } else {
+            const uint32_t w = (uint32_t)(vmask >> c0);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], (w >> j) & 1u ? __uint_as_float(v[j]) : -3.0e38f);
           }
-          m_loc = fmaxf(m_loc, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])));
+          // the scale is positive, so it commutes with the maximum
+          m_loc = fmaxf(m_loc, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2e);
         }
+        m_loc = fmaxf(m_loc, -1e30f);
       }
       xchg[half * 128 + r] = m_loc;
       named_barrier_sync(1 + q, 64);      // the two warps of this lane quarter
@@ -229,35 +250,43 @@ __global__ void __launch_bounds__(AttnTcCfg::THREADS, 1) attention_tc_kernel(con
       // pass 2: probabilities -> bf16 P tile `half` in the swizzled K-major layout, row sum
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
       uint8_t* tile = sP_ptr + half * 16384 + r * 128;
+      if (none_vis) {
 #pragma unroll
-      for (int c0 = 0; c0 < 64; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(tmem_S + lane_off + half * 64 + c0, v);
-        tmem_ld_wait();
-        uint32_t pk[16];
+        for (int cidx = 0; cidx < 8; ++cidx) *reinterpret_cast<uint4*>(tile + (cidx << 4)) = make_uint4(0u, 0u, 0u, 0u);
+      } else {
+        auto pass2 = [&](auto av) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float e[2];
+          for (int c0 = 0; c0 < 64; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(tmem_S + lane_off + half * 64 + c0, v);
+            tmem_ld_wait();
+            const uint32_t w = (uint32_t)(vmask >> c0);
+            uint32_t pk[16];
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int key = key0 + c0 + j + u;
-            const bool vis = (key < lim1) | ((key >= lo2) & (key <= hi2));
-            e[u] = vis ? ex2_approx(__uint_as_float(v[j + u]) * p.scale_log2e - m_new) : 0.f;
+            for (int j = 0; j < 32; j += 2) {
+              float e[2];
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                const float ex = ex2_approx(fmaf(__uint_as_float(v[j + u]), p.scale_log2e, -m_new));
+                e[u] = (decltype(av)::value || ((w >> (j + u)) & 1u)) ? ex : 0.f;
+              }
+              const __nv_bfloat162 h = __floats2bfloat162_rn(e[0], e[1]);
+              // the row sum uses the rounded probabilities, i.e. exactly what the PV product sees
+              ls[(j >> 1) & 3] += __bfloat162float(h.x) + __bfloat162float(h.y);
+              pk[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int cidx = (c0 >> 3) + g;   // 16-byte chunk of the 128-byte row
+              *reinterpret_cast<uint4*>(tile + ((cidx ^ (r & 7)) << 4)) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+            }
           }
-          const __nv_bfloat162 h = __floats2bfloat162_rn(e[0], e[1]);
-          // the row sum uses the rounded probabilities, i.e. exactly what the PV product sees
-          ls[(j >> 1) & 3] += __bfloat162float(h.x) + __bfloat162float(h.y);
-          pk[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
-        }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int cidx = (c0 >> 3) + g;   // 16-byte chunk of the 128-byte row
-          *reinterpret_cast<uint4*>(tile + ((cidx ^ (r & 7)) << 4)) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
-        }
+        };
+        if (all_vis) pass2(std::true_type{}); else pass2(std::false_type{});
       }
       l_run = l_run * alpha + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
       m_run = m_new;
-      if (c > 0) {   // rescale this thread's half of the running output (the previous PV MMAs completed before s_full)
+      if (c > 0 && warp_live) {   // rescale this thread's half of the running output (the previous PV MMAs completed before s_full)
 #pragma unroll 1
         for (int c0 = 0; c0 < 128; c0 += 32) {
           uint32_t v[32];
@@ -318,72 +347,75 @@ __global__ void __launch_bounds__(AttnTcCfg::THREADS, 1) attention_tc_kernel(con
     float* cl = p.scratch + (size_t)blockIdx.y * ksplit * C::SCOLS * 128;
     if (is_sm) {
       float* mine = cl + (size_t)rank * C::SCOLS * 128;
-      if (ok && n_chunks > 0) {
-#pragma unroll 1
-        for (int c0 = 0; c0 < 128; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(tmem_O + lane_off + half * 128 + c0, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) __stcg(mine + (half * 128 + c0 + j) * 128 + r, __uint_as_float(v[j]));
-        }
-      }
-      // a split without chunks contributes (max = -1e30, sums = 0) and gets zero weight
       const bool live = ok && n_chunks > 0;
-      if (half == 0) __stcg(mine + 256 * 128 + r, live ? m_run : -1e30f);
-      __stcg(mine + (257 + half) * 128 + r, live ? l_run : 0.f);
+      if (warp_live) {   // rows beyond n_q are never read back
+        if (live) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < 128; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(tmem_O + lane_off + half * 128 + c0, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) __stcg(mine + (half * 128 + c0 + j) * 128 + r, __uint_as_float(v[j]));
+          }
+        }
+        // a split without chunks contributes (max = -1e30, sums = 0) and gets zero weight
+        if (half == 0) __stcg(mine + 256 * 128 + r, live ? m_run : -1e30f);
+        __stcg(mine + (257 + half) * 128 + r, live ? l_run : 0.f);
+      }
     }
     __syncwarp();
     KTRACE_B(28, 64, p.ksplit - 1);
     cluster_sync_all();
     KTRACE_B(29, 64, p.ksplit - 1);
-    if (is_sm && i < p.n_q) {
-      // this CTA finishes the head-dim slice [d0, d0 + width) of all rows; the two threads of a row take half each
-      const int width = 256 / ksplit, hw = width >> 1, d0 = rank * width + half * hw;
-      float w[8];
-      float m_tot = -1e30f, l_tot = 0.f;
-      {
-        float mr[8], lr[8];
+    if (is_sm) {
+      // This CTA finishes the head-dim slice [rank * width, (rank + 1) * width) of every live row.  One item =
+      // one row x 8 consecutive outputs; items are spread over all 256 threads (the TMEM lane rule no longer
+      // binds a row to a warp here) and every load of an item is issued before the first use, so the merge
+      // costs one L2 round trip.
+      const int rows_here = min(128, p.n_q - row0);
+      const int rstride = rows_here <= 32 ? 32 : (rows_here <= 64 ? 64 : 128);
+      const int width = 256 / ksplit;
+      const int n_items = rstride * (width >> 3);
+      for (int item = (int)threadIdx.x - 64; item < n_items; item += 256) {
+        const int rr = item & (rstride - 1);
+        const int d0 = rank * width + (item / rstride) * 8;
+        if (rr >= rows_here) continue;
+        float mr[8], lr[8], a[8][8];
 #pragma unroll
-        for (int s = 0; s < 8; ++s) {
-          mr[s] = -1e30f;
-          lr[s] = 0.f;
-          if (s < ksplit) {
-            const float* src = cl + (size_t)s * C::SCOLS * 128;
-            mr[s] = __ldcg(src + 256 * 128 + r);
-            lr[s] = __ldcg(src + 257 * 128 + r) + __ldcg(src + 258 * 128 + r);
+        for (int s2 = 0; s2 < 8; ++s2) {
+          mr[s2] = -1e30f;
+          lr[s2] = 0.f;
+          if (s2 < ksplit) {
+            const float* src = cl + (size_t)s2 * C::SCOLS * 128;
+            mr[s2] = __ldcg(src + 256 * 128 + rr);
+            lr[s2] = __ldcg(src + 257 * 128 + rr) + __ldcg(src + 258 * 128 + rr);
           }
+#pragma unroll
+          for (int e = 0; e < 8; ++e) a[s2][e] = (s2 < ksplit) ? __ldcg(cl + ((size_t)s2 * C::SCOLS + d0 + e) * 128 + rr) : 0.f;
         }
+        float m_tot = -1e30f, l_tot = 0.f, w[8];
 #pragma unroll
-        for (int s = 0; s < 8; ++s) m_tot = fmaxf(m_tot, mr[s]);
+        for (int s2 = 0; s2 < 8; ++s2) m_tot = fmaxf(m_tot, mr[s2]);
 #pragma unroll
-        for (int s = 0; s < 8; ++s) {
-          w[s] = lr[s] > 0.f ? ex2_approx(mr[s] - m_tot) : 0.f;
-          l_tot += lr[s] * w[s];
+        for (int s2 = 0; s2 < 8; ++s2) {
+          w[s2] = lr[s2] > 0.f ? ex2_approx(mr[s2] - m_tot) : 0.f;
+          l_tot += lr[s2] * w[s2];
         }
-      }
-      const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-      bf16* orow = p.o + (size_t)i * p.ldo + d0;
-      for (int d = 0; d < hw; d += 8) {
-        float a[8][8];
-#pragma unroll
-        for (int s = 0; s < 8; ++s)
-#pragma unroll
-          for (int e = 0; e < 8; ++e)
-            a[s][e] = (s < ksplit) ? __ldcg(cl + ((size_t)s * C::SCOLS + d0 + d + e) * 128 + r) : 0.f;
+        const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
         float o[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           o[e] = 0.f;
 #pragma unroll
-          for (int s = 0; s < 8; ++s) o[e] += a[s][e] * w[s];
+          for (int s2 = 0; s2 < 8; ++s2) o[e] += a[s2][e] * w[s2];   // fixed rank order
         }
         uint4 wv;
         wv.x = pack_bf16(o[0] * inv, o[1] * inv);
         wv.y = pack_bf16(o[2] * inv, o[3] * inv);
         wv.z = pack_bf16(o[4] * inv, o[5] * inv);
         wv.w = pack_bf16(o[6] * inv, o[7] * inv);
-        *reinterpret_cast<uint4*>(orow + d) = wv;
+        *reinterpret_cast<uint4*>(p.o + (size_t)(row0 + rr) * p.ldo + d0) = wv;
       }
     }
   }
