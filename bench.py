@@ -33,6 +33,8 @@ WORKLOADS = {
     "cfg1": dict(model="pi0", num_views=1, prompt_len=0, chunk=50, seed=0),
     "cfg2": dict(model="pi0", num_views=3, prompt_len=20, chunk=50, seed=0),
     "cfg3": dict(model="pi05", num_views=2, prompt_len=52, chunk=50, seed=1),
+    # action expert alone over a prefilled K/V cache (the weight-streaming stage): stage mask 4 of the forward
+    "cfg4": dict(model="pi0", num_views=3, prompt_len=20, chunk=50, seed=0, stages=4),
     # throughput mode: 32 independent observations per forward on each GPU
     "cfg5": dict(model="pi0", num_views=2, prompt_len=20, chunk=50, seed=0, batch=32),
 }
@@ -40,7 +42,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from the ncu
 # capture summarised under profiles/), keyed by workload; None until a capture exists.
-NCU_TRAFFIC_BYTES = {"cfg2": 144486144, "cfg1": None, "cfg3": None, "cfg5": None}   # profiles/gemm_sm100_geglu_prefix_p788.md
+NCU_TRAFFIC_BYTES = {"cfg2": 144486144, "cfg1": None, "cfg3": None, "cfg4": None, "cfg5": None}   # profiles/gemm_sm100_geglu_prefix_p788.md
 
 
 def peaks():
@@ -223,6 +225,12 @@ def oracle_forward_fn(wl, ck):
     images, state, noise = [t.cpu() for t in inputs(wl, "cpu")]
     if wl.get("batch", 1) > 1:      # the oracle has no batch dimension: one observation of the batch per step
         images, state, noise = images[0], state[0], noise[0]
+    if wl.get("stages") == 4:       # expert alone: the prefix K/V cache is computed once, outside the timed calls
+        wf = O._weights_f32(w, "cpu")
+        vx = O.vision_encoder(wf, images.float())
+        enc = torch.cat([O.project_vision(wf, vx), wf["language_embeds"].reshape(-1, 2048)], 0)
+        K, V = O.prefix_encoder(wf, enc)
+        return lambda: O.pi0_decoder(wf, K, V, state.float(), noise.float())
     if wl["model"] == "pi0":
         return lambda: O.pi0_forward(w, images, state, noise)
     return lambda: O.pi05_forward(w, images, noise)
@@ -270,6 +278,79 @@ def run_reference(args, wl, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_latency_mode(args, wl, rank, world, local, device, dist):
+    """Multi-view latency mode: rank v < num_views runs the SigLIP tower of view v, the projected tiles are
+    gathered over NCCL into rank 0, which runs the prefix prefill and the action expert."""
+    import multi_gpu as M
+    nv = wl["num_views"]
+    if world < nv or wl["model"] != "pi0":
+        raise SystemExit("--mode latency needs a Pi0 workload and one rank per view (%d views, %d ranks)" % (nv, world))
+    ck = fast_checkpoint("pi0", wl["prompt_len"], wl["seed"], device)
+    Tower, Trunk = M.gpu_factories(ck, nv, wl["chunk"], device=local, flags=args.flags)
+    runner = M.MultiViewLatencyPi0(nv, Tower, Trunk)
+    images, state, noise = inputs(wl, device)
+    host_args = [t.cpu().pin_memory() for t in (images, state, noise)]
+    step = lambda: runner.forward(images, state, noise)
+
+    def barrier():
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    total_ms = e0.elapsed_time(e1)
+    lat = []
+    for _ in range(args.steps):
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        step()
+        b.record()
+        torch.cuda.synchronize()
+        lat.append(a.elapsed_time(b))
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        out = runner.forward(*host_args)
+        if out is not None:
+            out.cpu()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms, e2e_ms = max_over_ranks(dist, device, [total_ms, e2e_s * 1e3])
+    if rank == 0:
+        # rank 0 launches its own tower (vision stage of a 1-view engine) and the trunk's prefix + expert stages
+        n_trunk = runner.tower.infer._engine.stage_kernels()[0] + sum(runner.trunk.infer._engine.stage_kernels()[1:])
+        line = {"metric": "observations_per_s", "value": round(args.steps / (total_ms * 1e-3), 3), "unit": "obs/s",
+                "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": round(total_ms / args.steps, 4),
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": args.workload, **{k: wl[k] for k in ("model", "num_views", "prompt_len", "chunk")},
+                           "euler_steps": 10, "batch_per_gpu": 1,
+                           "parallelism": "latency mode: %d SigLIP towers on %d GPUs, NCCL gather of the projected tiles, prefix + expert on rank 0" % (nv, nv)},
+                "latency_ms": {"p50": round(percentile(lat, 0.5), 4), "p99": round(percentile(lat, 0.99), 4),
+                               "note": "rank 0, device events around tower + gather + prefix + expert"},
+                "e2e": {"value": round(args.steps / (e2e_ms * 1e-3), 3), "unit": "obs/s",
+                        "h2d_bytes_per_step": sum(x.numel() * 2 for x in host_args), "d2h_bytes_per_step": wl["chunk"] * 32 * 2,
+                        "ms_per_step": round(e2e_ms / args.steps, 4)},
+                "gpu_launches": n_trunk * args.steps, "clocks": clocks}
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -278,6 +359,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--mode", default="replicas", choices=["replicas", "latency"],
+                    help="replicas: every rank runs whole forwards (default); latency: one observation, one SigLIP tower "
+                         "per rank + gather (needs at least num_views ranks)")
     ap.add_argument("--flags", type=int, default=0, help="vla_config.flags: 1 = no programmatic dependent launch, 2 = no CUDA graph")
     ap.add_argument("--microbench", nargs="?", const="geglu", default=None, choices=["geglu", "expert_down", "expert_attention"],
                     help="time one kernel alone and print its roofline object: geglu = the dominant kernel of the workload "
@@ -310,6 +394,12 @@ def main():
         dist = dist_mod
         dist.init_process_group("nccl", device_id=device)
 
+    if args.mode == "latency":
+        if dist is None:
+            raise SystemExit("--mode latency needs torchrun with at least num_views ranks")
+        run_latency_mode(args, wl, rank, world, local, device, dist)
+        return
+
     if wl["model"] == "pi0":
         from pi0_infer import Pi0Inference
         ck = fast_checkpoint("pi0", wl["prompt_len"], wl["seed"], device)
@@ -318,6 +408,21 @@ def main():
         step = lambda: infer.forward(images, state, noise)
         host_args = [t.cpu().pin_memory() for t in (images, state, noise)]
         host_step = lambda: infer.forward_host(*host_args)
+        if wl.get("stages"):
+            # stage subset (the expert alone): one full forward fills the K/V cache, then every step copies the
+            # noise in and replays only that stage; the host-memory figure keeps the same subset
+            step()
+            noise_buf, mask, host_noise = infer.buffers["diffusion_noise"], wl["stages"], host_args[2]
+
+            def step():
+                noise_buf.copy_(noise)
+                infer._engine.forward_stages(mask)
+
+            def host_step():
+                noise_buf.copy_(host_noise, non_blocking=True)
+                infer._engine.forward_stages(mask)
+                return noise_buf.cpu()
+            host_args = [host_noise]
     else:
         from pi05_infer import Pi05Inference
         ck = fast_checkpoint("pi05", wl["prompt_len"], wl["seed"], device)
@@ -327,6 +432,8 @@ def main():
         host_args = [t.cpu().pin_memory() for t in (images, noise)]
         host_step = lambda: infer.forward_host(*host_args)
     n_kernels, dev_bytes = infer._engine.stats()
+    if wl.get("stages"):
+        n_kernels = sum(n for i, n in enumerate(infer._engine.stage_kernels()) if wl["stages"] >> i & 1)
     if args.profile_forward:
         step()
         torch.cuda.synchronize()
@@ -403,8 +510,15 @@ def main():
                 "clocks": clocks}
         del infer
         torch.cuda.empty_cache()
-        line["roofline"] = dominant_kernel_roofline(wl, device)
-        line["roofline"]["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload)
+        if wl.get("stages") == 4:
+            # the stage is a chain of ~930 launches, so the bound is stated for the stage as a whole: its
+            # algorithmic weight + K/V stream against the HBM copy peak (no single kernel dominates)
+            line["config"]["stages"] = "action expert only (stage mask 4), K/V cache prefilled by one forward"
+            line["roofline"] = dict(decoder_stream(wl, total_ms / args.steps), kernel="action-expert stage, 10 Euler steps", traffic=None)
+            line["decoder_stream"] = None
+        else:
+            line["roofline"] = dominant_kernel_roofline(wl, device)
+            line["roofline"]["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload)
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(wl, ck)
         print(json.dumps(line), flush=True)

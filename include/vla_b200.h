@@ -100,6 +100,9 @@ int vla_status_word(vla_handle h, int* out);
 /* Number of kernel launches in one forward, and device bytes held. */
 int vla_stats(vla_handle h, int* n_kernels, size_t* device_bytes);
 
+/* Kernel launches of one forward per stage: vision, prefix, decoder (their sum is vla_stats' n_kernels). */
+int vla_stage_kernels(vla_handle h, int* n3);
+
 /* Per-stage device time of one forward (ms, CUDA events, outside the graph): vision, prefix, decoder. */
 int vla_time_stages(vla_handle h, float* ms3);
 

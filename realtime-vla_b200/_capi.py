@@ -63,6 +63,7 @@ EXPORTS = {
     "vla_status_word": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
     "vla_stats": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_size_t)]),
     "vla_time_stages": (C.c_int, [C.c_void_p, C.POINTER(C.c_float)]),
+    "vla_stage_kernels": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
     "vla_destroy": (C.c_int, [C.c_void_p]),
     "vla_last_error": (C.c_char_p, [C.c_void_p]),
     "vla_op_gemm": (C.c_int, [C.POINTER(GemmDesc), C.c_void_p]),

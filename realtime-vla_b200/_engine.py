@@ -132,6 +132,12 @@ class Engine:
         _capi.check(self.lib.vla_stats(self.handle, C.byref(n), C.byref(b)), self.handle)
         return n.value, b.value
 
+    def stage_kernels(self):
+        """Kernel launches of one forward per stage: [vision, prefix, expert]."""
+        n = (C.c_int * 3)()
+        _capi.check(self.lib.vla_stage_kernels(self.handle, n), self.handle)
+        return list(n)
+
     def time_stages(self):
         ms = (C.c_float * 3)()
         _capi.check(self.lib.vla_time_stages(self.handle, ms), self.handle)

@@ -1153,6 +1153,14 @@ int vla_stats(vla_handle m, int* n_kernels, size_t* device_bytes) {
   return VLA_OK;
 }
 
+int vla_stage_kernels(vla_handle m, int* n3) {
+  if (!m || !m->finalized || !n3) return VLA_ERR_STATE;
+  n3[0] = n3[1] = n3[2] = 0;
+  for (const auto& op : m->ops)
+    if (op.is_kernel && op.stage >= 0 && op.stage < 3) n3[op.stage]++;
+  return VLA_OK;
+}
+
 int vla_time_stages(vla_handle m, float* ms3) {
   if (!m || !m->finalized || !ms3) return VLA_ERR_STATE;
   cudaSetDevice(m->cfg.device);
