@@ -24,7 +24,8 @@ class GemmDesc(C.Structure):
                 ("out_f32", C.c_void_p), ("res", C.c_void_p), ("gate", C.c_void_p), ("res_mod", C.c_int),
                 ("q", C.c_void_p), ("kcache", C.c_void_p), ("vcache", C.c_void_p), ("vt", C.c_void_p), ("vt_ld", C.c_int),
                 ("pos_off", C.c_int), ("rows_per_obs", C.c_int), ("kv_obs_stride", C.c_int), ("kv_row_off", C.c_int),
-                ("split", C.c_int), ("bn", C.c_int), ("iters", C.c_int), ("ms_per_iter", C.POINTER(C.c_float))]
+                ("split", C.c_int), ("bn", C.c_int), ("iters", C.c_int), ("ms_per_iter", C.POINTER(C.c_float)),
+                ("pair", C.c_int)]
 
 
 class AttnDesc(C.Structure):

@@ -86,6 +86,8 @@ struct GemmParams {
   int n_tok;         // valid tokens
   int k_blocks;      // Kp / 64
   int split;         // cluster size along K (1 = no cluster)
+  int m256;          // launch of the PAIR variant: the two accumulators are two feature tiles of ONE weight
+                     // (features feat0.. and feat0+128..) instead of the gate/up pair; each gets the plain epilogue
   int* status;       // device status word
   float* scratch;    // split-K partial tiles: [tile][src rank][accumulator][column][128 features] fp32
   long long* trace;  // development timeline (see GEMM_TRACE), normally null
@@ -252,9 +254,14 @@ __device__ __forceinline__ void gemm_epilogue_cols(const GemmEpi& e, const EpiTh
   }
 }
 
-template <int BN, bool DUAL, bool SPLITK>
+// DUAL: gate/up pair of two weights (GeGLU).  PAIR: two 128-feature tiles of one weight, each with the plain
+// epilogue.  Both keep two accumulators that share the activation tile (TWO).
+template <int BN, bool DUAL, bool SPLITK, bool PAIR = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
-  using C = GemmCfg<BN, DUAL, SPLITK>;
+  static_assert(!(DUAL && PAIR), "a paired launch has one weight");
+  constexpr bool TWO = DUAL || PAIR;
+  constexpr bool m256 = PAIR;
+  using C = GemmCfg<BN, TWO, SPLITK>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -275,7 +282,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   const int split = SPLITK ? p.split : 1;
   const int rank = SPLITK ? (int)blockIdx.x : 0;  // == cluster rank: cluster dims are (split,1,1), gridDim.x == split
   const int tok0 = blockIdx.y * BN;
-  const int feat0 = blockIdx.z * 128;
+  const int feat0 = blockIdx.z * (m256 ? 256 : 128);
   const int kb_begin = (int)(((long long)rank * p.k_blocks) / split);
   const int kb_end = (int)(((long long)(rank + 1) * p.k_blocks) / split);
   const int n_iters = kb_end - kb_begin;
@@ -316,7 +323,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       const int k0 = (kb_begin + it) * 64;
       mbar_expect_tx(full_bar + 8 * it, C::STAGE_BYTES);
       tma_load_2d(st, &p.tmA, full_bar + 8 * it, k0, feat0, pol_w);
-      if (DUAL) tma_load_2d(st + C::A_BYTES, &p.tmA2, full_bar + 8 * it, k0, feat0, pol_w);
+      if (TWO) tma_load_2d(st + C::A_BYTES, m256 ? &p.tmA : &p.tmA2, full_bar + 8 * it, k0, feat0 + (m256 ? 128 : 0), pol_w);
     }
   }
   // Activations (and everything the epilogue reads or writes) do.
@@ -336,9 +343,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           if (!mbar_wait(empty_bar + 8 * s, ph ^ 1u, abort_flag)) break;
           mbar_expect_tx(full_bar + 8 * s, C::STAGE_BYTES);
           tma_load_2d(st, &p.tmA, full_bar + 8 * s, k0, feat0, pol_w);
-          if (DUAL) tma_load_2d(st + C::A_BYTES, &p.tmA2, full_bar + 8 * s, k0, feat0, pol_w);
+          if (TWO) tma_load_2d(st + C::A_BYTES, m256 ? &p.tmA : &p.tmA2, full_bar + 8 * s, k0, feat0 + (m256 ? 128 : 0), pol_w);
         }
-        tma_load_2d(st + C::A_BYTES * (DUAL ? 2 : 1), &p.tmB, full_bar + 8 * s, k0, tok0, pol_x);
+        tma_load_2d(st + C::A_BYTES * (TWO ? 2 : 1), &p.tmB, full_bar + 8 * s, k0, tok0, pol_x);
       }
       GEMM_TRACE(3);
     }
@@ -359,12 +366,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         const uint32_t st = smem_base + s * C::STAGE_BYTES;
         const uint64_t da = umma_desc_sw128(st);
         const uint64_t da2 = umma_desc_sw128(st + C::A_BYTES);
-        const uint64_t db = umma_desc_sw128(st + C::A_BYTES * (DUAL ? 2 : 1));
+        const uint64_t db = umma_desc_sw128(st + C::A_BYTES * (TWO ? 2 : 1));
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           const uint32_t acc = (it | kk) != 0;
           umma_bf16(tmem_base, da + 2 * kk, db + 2 * kk, idesc, acc);
-          if (DUAL) umma_bf16(tmem_base + BN, da2 + 2 * kk, db + 2 * kk, idesc, acc);
+          if (TWO) umma_bf16(tmem_base + BN, da2 + 2 * kk, db + 2 * kk, idesc, acc);
         }
         umma_commit(empty_bar + 8 * s);  // frees this smem stage once the MMAs have read it
       }
@@ -394,12 +401,20 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   const int fl = q * 32 + lane;           // feature lane 0..127
   const int n = feat0 + fl;
   const bool n_ok = n < p.n_feat;
-  EpiThread th;   // per-feature constants, fetched while the main loop runs
-  th.n = n;
-  th.n_ok = n_ok;
-  th.bias = (is_epi && n_ok && p.epi.bias) ? p.epi.bias[n] : 0.f;
-  th.gate = (is_epi && n_ok && p.epi.gate) ? p.epi.gate[n] : 1.f;
-  th.pos_base = (p.epi.kind == EPI_QKV && p.epi.pos_base) ? *p.epi.pos_base : 0;
+  EpiThread th_first;   // per-feature constants, fetched while the main loop runs
+  th_first.n = n;
+  th_first.n_ok = n_ok;
+  th_first.bias = (is_epi && n_ok && p.epi.bias) ? p.epi.bias[n] : 0.f;
+  th_first.gate = (is_epi && n_ok && p.epi.gate) ? p.epi.gate[n] : 1.f;
+  th_first.pos_base = (p.epi.kind == EPI_QKV && p.epi.pos_base) ? *p.epi.pos_base : 0;
+  EpiThread th2 = th_first;   // second feature tile of an m256 launch
+  if (m256) {
+    th2.n = n + 128;
+    th2.n_ok = th2.n < p.n_feat;
+    th2.bias = (is_epi && th2.n_ok && p.epi.bias) ? p.epi.bias[th2.n] : 0.f;
+    th2.gate = (is_epi && th2.n_ok && p.epi.gate) ? p.epi.gate[th2.n] : 1.f;
+  }
+  const int n_pass = m256 ? 2 : 1;
   bool acc_ok = false;
   if (is_epi) {
     acc_ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar, 0, abort_flag));   // TMEM loads are warp-collective
@@ -418,12 +433,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       const bool f32 = p.out_mode == 2 || p.out_mode == 3;
       uint8_t* stg = smem + (warp - 2) * 8192;              // two 4 KB slots per warp
       const uint32_t stg_addr = smem_base + (warp - 2) * 8192;
-      const int x0 = feat0 + q * 32;
       int it = 0;
+#pragma unroll 1
+      for (int pass = 0; pass < n_pass; ++pass) {
+      const EpiThread& th = pass ? th2 : th_first;
+      const int n = th.n;
+      const int x0 = feat0 + pass * 128 + q * 32;
       for (int c0 = 32 * half; c0 < umma_n; c0 += 64, ++it) {
         uint32_t v[32], v2[32];
         if (threadIdx.x == 64 && c0 == 0) GEMM_TRACE(7);
-        tmem_ld32(t_lane + c0, v);
+        tmem_ld32(t_lane + pass * BN + c0, v);
         if (DUAL) tmem_ld32(t_lane + BN + c0, v2);
         tmem_ld_wait();
         if (threadIdx.x == 64 && c0 == 0) GEMM_TRACE(8);
@@ -502,37 +521,45 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         }
         fence_proxy_async_shared();
         __syncwarp();
-        if (lane == 0 && x0 < p.n_feat) {
-          if (p.out_mode == 3) tma_reduce_add_2d(&p.tmOut, stg_addr + slot * 4096, x0, tok0 + c0);
-          else if (p.out_mode == 4 && x0 >= 2304) tma_store_2d(&p.tmOut3, stg_addr + slot * 4096, x0 - 2304, p.epi.kv_row_off + tok0 + c0);
-          else if (p.out_mode == 4 && x0 >= 2048) tma_store_2d(&p.tmOut2, stg_addr + slot * 4096, x0 - 2048, p.epi.kv_row_off + tok0 + c0);
-          else tma_store_2d(&p.tmOut, stg_addr + slot * 4096, x0, tok0 + c0);
+        if (lane == 0) {
+          if (x0 < p.n_feat) {
+            if (p.out_mode == 3) tma_reduce_add_2d(&p.tmOut, stg_addr + slot * 4096, x0, tok0 + c0);
+            else if (p.out_mode == 4 && x0 >= 2304) tma_store_2d(&p.tmOut3, stg_addr + slot * 4096, x0 - 2304, p.epi.kv_row_off + tok0 + c0);
+            else if (p.out_mode == 4 && x0 >= 2048) tma_store_2d(&p.tmOut2, stg_addr + slot * 4096, x0 - 2048, p.epi.kv_row_off + tok0 + c0);
+            else tma_store_2d(&p.tmOut, stg_addr + slot * 4096, x0, tok0 + c0);
+          }
+          // one group per chunk even when nothing is stored (feature padding, the empty second tile of a paired
+          // launch): the slot reuse above counts groups
           bulk_commit();
         }
         if (threadIdx.x == 64 && c0 == 0) GEMM_TRACE(9);
       }
+      }
       if (lane == 0) bulk_wait_all();
       __syncwarp();
     } else if (is_epi && acc_ok) {
-      for (int c0 = 32 * half; c0 < umma_n; c0 += 64) {
-        uint32_t v[32], v2[32];
-        tmem_ld32(t_lane + c0, v);
-        if (DUAL) tmem_ld32(t_lane + BN + c0, v2);
-        tmem_ld_wait();
-        if (scaled) {
+#pragma unroll 1
+      for (int pass = 0; pass < n_pass; ++pass) {
+        for (int c0 = 32 * half; c0 < umma_n; c0 += 64) {
+          uint32_t v[32], v2[32];
+          tmem_ld32(t_lane + pass * BN + c0, v);
+          if (DUAL) tmem_ld32(t_lane + BN + c0, v2);
+          tmem_ld_wait();
+          if (scaled) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            v[j] = __float_as_uint(__uint_as_float(v[j]) * row_scale[c0 + j]);
-            if (DUAL) v2[j] = __float_as_uint(__uint_as_float(v2[j]) * row_scale[c0 + j]);
+            for (int j = 0; j < 32; ++j) {
+              v[j] = __float_as_uint(__uint_as_float(v[j]) * row_scale[c0 + j]);
+              if (DUAL) v2[j] = __float_as_uint(__uint_as_float(v2[j]) * row_scale[c0 + j]);
+            }
           }
+          const int n_valid = min(32, p.n_tok - (tok0 + c0));
+          gemm_epilogue_cols<32>(p.epi, pass ? th2 : th_first, tok0 + c0, 1, n_valid, reinterpret_cast<const float*>(v),
+                                 reinterpret_cast<const float*>(m256 ? v : v2));
         }
-        const int n_valid = min(32, p.n_tok - (tok0 + c0));
-        gemm_epilogue_cols<32>(p.epi, th, tok0 + c0, 1, n_valid, reinterpret_cast<const float*>(v),
-                               reinterpret_cast<const float*>(v2));
       }
     }
   } else {
-    constexpr int ACCS = DUAL ? 2 : 1;
+    constexpr int ACCS = TWO ? 2 : 1;
     const int n_cols = min(umma_n, p.n_tok - tok0);
     // scratch of this cluster: [src rank][accumulator][column][128 features]
     float* tile_scratch = p.scratch + (size_t)(blockIdx.z * gridDim.y + blockIdx.y) * split * C::PARTIAL_FLOATS;
@@ -571,7 +598,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
             b[r] = 0.f;
             if (r < split && i0 + ci < n_owned) {
               a[r] = __ldcg(tile_scratch + (size_t)r * C::PARTIAL_FLOATS + c * 128 + fl);
-              if (DUAL) b[r] = __ldcg(tile_scratch + (size_t)r * C::PARTIAL_FLOATS + (BN + c) * 128 + fl);
+              if (TWO) b[r] = __ldcg(tile_scratch + (size_t)r * C::PARTIAL_FLOATS + (BN + c) * 128 + fl);
             }
           }
           s1[ci] = ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
@@ -583,7 +610,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           }
         }
         const int n_valid = min(4, n_owned - i0);
-        gemm_epilogue_cols<4>(p.epi, th, tok0 + rank + i0 * split, split, n_valid, s1, s2);
+        if (m256) {
+          gemm_epilogue_cols<4>(p.epi, th_first, tok0 + rank + i0 * split, split, n_valid, s1, s1);
+          gemm_epilogue_cols<4>(p.epi, th2, tok0 + rank + i0 * split, split, n_valid, s2, s2);
+        } else {
+          gemm_epilogue_cols<4>(p.epi, th_first, tok0 + rank + i0 * split, split, n_valid, s1, s2);
+        }
       }
     }
     if (threadIdx.x == 64) GEMM_TRACE(9);

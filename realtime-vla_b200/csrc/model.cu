@@ -148,45 +148,59 @@ int pick_split(int units, int k_blocks, int sm_count) {
 //   per-SM L2 read rate, measured 59-62 B/clk), the MMAs take 2*bn clk per accumulator, whichever is longer;
 //   + epilogue ~22 clk per token column and accumulator (two warps per lane quarter), + ~5000 clk for the
 //   split-K exchange; x the number of waves over the SMs.
-void pick_tiling(int tokens, int feat_tiles, int k_blocks, bool dual, int sm_count, int* bn, int* split) {
-  if (tokens <= 128) {
+// A single-weight GEMM may also pair two feature tiles in one CTA (m256: 256 features x bn tokens, two
+// accumulators sharing the activation tile like the gate/up pair): 32 KB + 128 B per token per K block for twice
+// the MMA work, which lifts 256-token tiles from TMA-bound (96 B/clk) to balanced (64 B/clk) at the price of half
+// as many CTAs and a twice larger split-K exchange.  m256_mode: 0 = let the model choose, 1 = force, -1 = never.
+void pick_tiling(int tokens, int feat_tiles, int k_blocks, bool dual, int sm_count, int* bn, int* split, int* m256,
+                 int m256_mode = 0) {
+  *m256 = 0;
+  if (tokens <= 128 && m256_mode <= 0) {
     *bn = tokens <= 64 ? 64 : 128;
     *split = pick_split(feat_tiles, k_blocks, sm_count);
     return;
   }
-  const int accs = dual ? 2 : 1;
   double best = 1e30;
   *bn = 256;
   *split = 1;
   // up to 256 tokens a 128-token tile always measured at least as fast as one 256-token tile (more CTAs, a
   // cheaper split-K exchange); dual-accumulator GEMMs keep 256 (their main loop is MMA-bound only there)
   const int b_max = (tokens <= 256 && !dual) ? 128 : 256;
-  for (int b = 128; b <= b_max; b *= 2) {
-    for (int s = 1; s <= 8; s *= 2) {
-      if (s > 1 && (k_blocks / s < 8)) continue;          // keep K slices long enough to amortise the exchange
-      const int tok_tiles = (tokens + b - 1) / b;
-      const long long ctas = (long long)feat_tiles * tok_tiles * s;
-      if (s > 1 && (size_t)ctas * 128 * b * accs > ((size_t)16 << 20)) continue;   // split-K scratch capacity (floats)
-      const int kb = (k_blocks + s - 1) / s;
-      const double load = kb * (16384.0 * accs + 128.0 * b) / 64.0;
-      const double mma = kb * 2.0 * b * accs;
-      const double epi = 22.0 * (b / 2) * accs;
-      const double exch = s > 1 ? 5000.0 * (b / 128) * accs : 0.0;     // partial tile through L2 + cluster barrier
-      const double cta = (load > mma ? load : mma) + epi + exch;
-      const int resident = s == 8 ? 128 : (s == 4 ? 144 : sm_count);  // clusters are scheduled whole within a GPC
-      const double waves = (double)((ctas + resident - 1) / resident);
-      const double cost = waves * cta;
-      if (cost < best) { best = cost; *bn = b; *split = s; }
+  for (int pair = 0; pair <= 1; ++pair) {
+    if (pair && (dual || m256_mode < 0 || feat_tiles < 2)) continue;
+    if (!pair && m256_mode > 0 && !dual && feat_tiles >= 2) continue;
+    const int accs = (dual || pair) ? 2 : 1;
+    const int ftiles = pair ? (feat_tiles + 1) / 2 : feat_tiles;
+    for (int b = 128; b <= (pair ? 256 : b_max); b *= 2) {
+      for (int s = 1; s <= 8; s *= 2) {
+        if (s > 1 && (k_blocks / s < 8)) continue;          // keep K slices long enough to amortise the exchange
+        const int tok_tiles = (tokens + b - 1) / b;
+        const long long ctas = (long long)ftiles * tok_tiles * s;
+        if (s > 1 && (size_t)ctas * 128 * b * accs > ((size_t)16 << 20)) continue;   // split-K scratch capacity (floats)
+        // measured: a paired tile only pays unsplit and over several waves (batched forwards: 788 x 16384 x 2048
+        // took 72 us paired with K split 4 against 68 us unpaired, 17 024 tokens 870 us against 1 076 us)
+        if (pair && m256_mode == 0 && (s > 1 || ctas < 2LL * sm_count)) continue;
+        const int kb = (k_blocks + s - 1) / s;
+        const double load = kb * (16384.0 * accs + 128.0 * b) / 64.0;
+        const double mma = kb * 2.0 * b * accs;
+        const double epi = 22.0 * (b / 2) * accs;
+        const double exch = s > 1 ? 5000.0 * (b / 128) * accs : 0.0;     // partial tile through L2 + cluster barrier
+        const double cta = (load > mma ? load : mma) + epi + exch;
+        const int resident = s == 8 ? 128 : (s == 4 ? 144 : sm_count);  // clusters are scheduled whole within a GPC
+        const double waves = (double)((ctas + resident - 1) / resident);
+        const double cost = waves * cta;
+        if (cost < best) { best = cost; *bn = b; *split = s; *m256 = pair; }
+      }
     }
   }
 }
 
-template <int BN, bool DUAL, bool SPLITK>
+template <int BN, bool DUAL, bool SPLITK, bool PAIR = false>
 cudaError_t launch_gemm_t(const GemmOp& op, cudaStream_t st, bool pdl) {
-  using C = GemmCfg<BN, DUAL, SPLITK>;
+  using C = GemmCfg<BN, DUAL || PAIR, SPLITK>;
   static_assert(C::VALID, "tile shape leaves fewer than 3 pipeline stages");
   static bool attr_set = false;
-  auto kern = gemm_sm100_kernel<BN, DUAL, SPLITK>;
+  auto kern = gemm_sm100_kernel<BN, DUAL, SPLITK, PAIR>;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) return e;
@@ -197,6 +211,11 @@ cudaError_t launch_gemm_t(const GemmOp& op, cudaStream_t st, bool pdl) {
 
 cudaError_t launch_gemm(const GemmOp& op, cudaStream_t st, bool pdl) {
   const bool sk = op.p.split > 1;
+  if (op.p.m256) {   // two feature tiles of one weight per CTA
+    if (op.bn == 64) return sk ? launch_gemm_t<64, false, true, true>(op, st, pdl) : launch_gemm_t<64, false, false, true>(op, st, pdl);
+    if (op.bn == 128) return sk ? launch_gemm_t<128, false, true, true>(op, st, pdl) : launch_gemm_t<128, false, false, true>(op, st, pdl);
+    return sk ? launch_gemm_t<256, false, true, true>(op, st, pdl) : launch_gemm_t<256, false, false, true>(op, st, pdl);
+  }
   if (op.bn == 64) {
     if (op.dual) return sk ? launch_gemm_t<64, true, true>(op, st, pdl) : launch_gemm_t<64, true, false>(op, st, pdl);
     return sk ? launch_gemm_t<64, false, true>(op, st, pdl) : launch_gemm_t<64, false, false>(op, st, pdl);
@@ -212,19 +231,26 @@ cudaError_t launch_gemm(const GemmOp& op, cudaStream_t st, bool pdl) {
 // w / w2: repacked weights [n_feat_pad, Kp]; x: activations [tokens, K] with pitch ldx.
 bool build_gemm(GemmOp* op, const bf16* w, const bf16* w2, int n_feat, int n_feat_pad, int Kp, const bf16* x, int tokens,
                 int Kx, int ldx, const GemmEpi& epi, int* status, int sm_count, int force_bn, int force_split,
-                std::string* err) {
+                std::string* err, int m256_mode = 0) {
   memset(op, 0, sizeof *op);
   op->dual = w2 != nullptr;
   if (Kp % 64 || n_feat_pad % 128) { *err = "repacked weight must be padded to 128 features x 64 K"; return false; }
-  const int feat_tiles = n_feat_pad / 128, kb = Kp / 64;
-  int bn, split;
-  pick_tiling(tokens, feat_tiles, kb, op->dual, sm_count, &bn, &split);
+  int feat_tiles = n_feat_pad / 128;
+  const int kb = Kp / 64;
+  int bn, split, m256;
+  pick_tiling(tokens, feat_tiles, kb, op->dual, sm_count, &bn, &split, &m256, m256_mode);
   if (force_bn > 0) {
     bn = force_bn;
     if (bn != 64 && bn != 128 && bn != 256) { *err = "token tile must be 64, 128 or 256"; return false; }
-    split = can_split(bn, op->dual) ? pick_split(feat_tiles * ((tokens + bn - 1) / bn), kb, sm_count) : 1;
+    m256 = (m256_mode > 0 && !op->dual && feat_tiles >= 2) ? 1 : 0;
+    split = can_split(bn, op->dual) ? pick_split((m256 ? (feat_tiles + 1) / 2 : feat_tiles) * ((tokens + bn - 1) / bn), kb, sm_count) : 1;
   }
   if (force_split > 0) split = force_split;
+  if (m256) {
+    op->dual = true;                       // two accumulators, both fed from `w`
+    feat_tiles = (feat_tiles + 1) / 2;
+  }
+  op->p.m256 = m256;
   op->bn = bn;
   const int tok_tiles = (tokens + bn - 1) / bn;
   if (split > 1 && !can_split(bn, op->dual)) { *err = "this tile shape has no split-K variant"; return false; }
@@ -1253,7 +1279,7 @@ int vla_op_gemm(const vla_gemm_desc* d, void* stream) {
     e.vt = reinterpret_cast<bf16*>(d->vt); e.vt_ld = d->vt_ld;
   }
   if (!build_gemm(&op, wt, wt2, d->N, Np, Kp, reinterpret_cast<const bf16*>(d->x), d->tokens, d->K, d->K, e, status, sms,
-                  d->bn, d->split, &err)) {
+                  d->bn, d->split, &err, d->pair)) {
     g_last_error = err;
     rc = VLA_ERR_SHAPE;
     goto done;
@@ -1391,7 +1417,7 @@ int vla_op_gemm_noalloc(const vla_gemm_noalloc_desc* d, void* stream) {
   GemmOp op;
   std::string err;
   if (!build_gemm(&op, reinterpret_cast<const bf16*>(d->w_nk), nullptr, d->N, d->n_pad, d->k_pad,
-                  reinterpret_cast<const bf16*>(d->x), d->tokens, d->K, d->K, e, nullptr, sms, 0, d->split, &err)) {
+                  reinterpret_cast<const bf16*>(d->x), d->tokens, d->K, d->K, e, nullptr, sms, 0, d->split, &err, -1)) {
     g_last_error = "vla_op_gemm_noalloc: " + err;
     return VLA_ERR_SHAPE;
   }

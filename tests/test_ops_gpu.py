@@ -146,6 +146,31 @@ def test_gemm_bias_bf16(tokens, K, N, split, bn):
     assert_close(out, x.float() @ w.float() + b, what="gemm+bias")
 
 
+# two 128-feature tiles of one weight per CTA (pair=1): bf16 / residual / QKV epilogues, with and without K split,
+# token tiles with a ragged edge, an odd number of feature tiles (the second tile of the last CTA is empty)
+@pytest.mark.parametrize("tokens,K,N,split,bn", [(788, 2048, 2048, 1, 256), (788, 4096, 2048, 4, 256), (300, 1152, 1152, 2, 128),
+                                                 (256, 1152, 4304, 1, 256), (600, 2048, 384, 1, 128), (51, 1024, 1024, 4, 64)])
+def test_gemm_pair_bias_bf16(tokens, K, N, split, bn):
+    import vla_ops as gpu_ops
+    d = dev()
+    x, w, b = rnd((tokens, K), 1.0, 42, d), rnd((K, N), 0.05, 43, d), rnd((N,), 0.5, 44, d).float()
+    out = gpu_ops.gemm(x, w, bias=b, split=split, bn=bn, pair=1)
+    assert_close(out, x.float() @ w.float() + b, what="paired gemm+bias")
+
+
+@pytest.mark.parametrize("tokens,K,N,split,gated", [(788, 16384, 2048, 4, False), (788, 2048, 2048, 1, True), (1576, 4304, 1152, 1, False)])
+def test_gemm_pair_residual(tokens, K, N, split, gated):
+    import vla_ops as gpu_ops
+    d = dev()
+    x, w = rnd((tokens, K), 1.0, 45, d), rnd((K, N), 0.02, 46, d)
+    res = rnd((tokens, N), 1.0, 47, d).float()
+    gate = rnd((N,), 1.0, 48, d).float() if gated else None
+    bias = rnd((N,), 0.5, 49, d).float()
+    out = gpu_ops.gemm(x, w, bias=bias, epi=1, res=res, gate=gate, split=split, bn=256, pair=1)
+    y = x.float() @ w.float()
+    assert_close(out, res + bias + (y * gate if gated else y), rel=1e-4, what="paired residual")
+
+
 @pytest.mark.parametrize("act", [1, 2])
 def test_gemm_activation(act):
     import vla_ops as gpu_ops
