@@ -59,7 +59,8 @@ int vla_create(const vla_config* cfg, vla_handle* out);
 /* Replaces `self.weights[k].copy_(v)` (pi0_infer.py:1337-1338, pi05_infer.py:666-668): `data` is a
  * contiguous host or device tensor of the checkpoint's shape ([in, out] weights, layers stacked on dim 0),
  * bf16 or fp32.  The library repacks it into its own layout.  Any subset of keys may be loaded; keys never
- * loaded stay zero.  'language_embeds' sets the prompt (rows <= prompt_len). */
+ * loaded stay zero.  'language_embeds' sets the prompt (rows <= prompt_len).  'embedding_weight' ((vocab, 2048),
+ * optional) is the token table used by vla_set_prompt_ids. */
 int vla_load_weight(vla_handle h, const char* key, const void* data, const int64_t* shape, int ndim, int dtype);
 
 /* Replaces the tail of the constructors: RoPE tables (pi0_infer.py:1319-1335), Pi05 out-projection scaling
@@ -70,6 +71,14 @@ int vla_finalize(vla_handle h);
  * (host or device) into the prompt window, sets the valid prefix length and the suffix RoPE start
  * (num_views*256 + len - 1).  For Pi0 it only replaces the prompt rows (len must equal prompt_len). */
 int vla_set_prompt(vla_handle h, const void* embeds_bf16, int len);
+
+/* Pi05 per-call prompt from token ids (pi05_infer.py:769-785: embedding(ids) * sqrt(2048) in bf16, then the
+ * copy into encoder_x, pi05_infer.py:819-822).  Needs the token table loaded with vla_load_weight under the key
+ * 'embedding_weight' ((vocab, 2048), the reference's optional checkpoint entry, pi05_infer.py:726-743) BEFORE
+ * vla_finalize: the gather then runs inside the captured graph and this call only copies `len` int32 ids (host or
+ * device memory) and three scalars.  Ids outside the table are clamped and raise the device status word.
+ * The tokenizer stays with the caller.  For Pi0 len must equal prompt_len. */
+int vla_set_prompt_ids(vla_handle h, const int32_t* ids, int len);
 
 /* Device address and size of a named library-owned buffer, so that a host framework can wrap it without a
  * copy: "observation_images_normalized" bf16 (batch,nv,224,224,3), "observation_state_normalized" bf16

@@ -297,6 +297,14 @@ def pi0_forward(checkpoint, images, state, noise, device="cpu", return_intermedi
     return out
 
 
+def pi05_prompt_from_ids(embedding_weight, ids):
+    """Prompt embeddings of token ids: embedding(ids) * sqrt(2048), rounded to bf16 as in the reference
+    (pi05_infer.py:726-743 builds the bf16 table, :783-785 gathers and scales).  Returns fp32 values."""
+    table = torch.as_tensor(embedding_weight).to(torch.bfloat16)
+    ids = torch.as_tensor(ids).long().cpu()
+    return (table.cpu()[ids] * float(table.shape[1] ** 0.5)).to(torch.bfloat16).float()
+
+
 @torch.no_grad()
 def pi05_forward(checkpoint, images, noise, device="cpu", prompt_embeds=None, max_prompt_len=None,
                  return_intermediates=False):

@@ -107,6 +107,11 @@ class Engine:
         embeds = embeds.detach().to(device=self.device, dtype=torch.bfloat16).contiguous()
         _capi.check(self.lib.vla_set_prompt(self.handle, C.c_void_p(embeds.data_ptr()), embeds.shape[0]), self.handle)
 
+    def set_prompt_ids(self, ids):
+        """Prompt as token ids (int, host or device): embedded on the device from 'embedding_weight', inside the graph."""
+        ids = torch.as_tensor(ids).detach().to(torch.int32).contiguous()
+        _capi.check(self.lib.vla_set_prompt_ids(self.handle, C.c_void_p(ids.data_ptr()), int(ids.numel())), self.handle)
+
     def forward(self):
         stream = torch.cuda.current_stream(self.device).cuda_stream
         _capi.check(self.lib.vla_forward(self.handle, C.c_void_p(stream)), self.handle)

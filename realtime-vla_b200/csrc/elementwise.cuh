@@ -133,6 +133,30 @@ __global__ void prompt_rows_kernel(const bf16* __restrict__ emb, float* __restri
   const size_t r = idx - (size_t)b * per;
   x[((size_t)b * P + row_off) * 2048 + r] = __bfloat162float(emb[r]);
 }
+// Prompt rows from token ids (pi05_infer.py:769-785: embedding(ids) * sqrt(2048), bf16): row r of the prompt
+// window gets bf16(table[ids[r]] * scale) for r < *n_ids and zeros beyond; *n_ids < 0 means the prompt rows
+// were given as embeddings and are left alone.  ids and n_ids live in device memory so that the kernel can sit
+// inside the captured graph.  An id outside the table is clamped and raises the status word.
+__global__ void prompt_from_ids_kernel(const bf16* __restrict__ table, int vocab, const int* __restrict__ ids,
+                                       const int* __restrict__ n_ids, bf16* __restrict__ emb, float scale, int* status) {
+  pdl_trigger();
+  pdl_wait();
+  const int n = *n_ids;
+  if (n < 0) return;
+  const int r = blockIdx.x;
+  bf16* dst = emb + (size_t)r * 2048;
+  if (r >= n) {
+    for (int c = threadIdx.x; c < 2048; c += blockDim.x) dst[c] = __float2bfloat16(0.f);
+    return;
+  }
+  int id = ids[r];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0 && status) atomicOr(status, VLA_ST_BAD_SHAPE);
+    id = min(max(id, 0), vocab - 1);
+  }
+  const bf16* src = table + (size_t)id * 2048;
+  for (int c = threadIdx.x; c < 2048; c += blockDim.x) dst[c] = __float2bfloat16(__bfloat162float(src[c]) * scale);
+}
 // dst rows (b*dst_stride + dst_off) <- src rows b, fp32, `width` columns
 __global__ void copy_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, int width, int dst_stride_rows,
                                  int dst_off_rows, int batch) {

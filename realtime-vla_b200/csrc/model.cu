@@ -416,6 +416,10 @@ struct vla_model {
   float *style_attn, *style_ffn, *style_fin;
   bf16 *time_tmp, *time_emb;
   int *d_valid_len, *d_pos_base, *d_status;
+  bf16* embed_table = nullptr;    // optional token embedding table [vocab, 2048] ('embedding_weight')
+  int vocab = 0;
+  int *d_ids = nullptr, *d_n_ids = nullptr;   // prompt token ids and their count (-1: prompt given as embeddings)
+  int n_ids = -1;
   float* gemm_scratch;            // split-K partial tiles of whichever GEMM is running (kernels never overlap)
   size_t gemm_scratch_cap = 0;    // floats
   float* attn_scratch;            // key-split partial outputs of whichever attention kernel is running
@@ -581,6 +585,8 @@ bool alloc_buffers(vla_model* m) {
   ok &= m->dalloc(&m->d_valid_len, 1);
   ok &= m->dalloc(&m->d_pos_base, 1);
   ok &= m->dalloc(&m->d_status, 1);
+  ok &= m->dalloc(&m->d_ids, (size_t)std::max(m->L, 1));
+  ok &= m->dalloc(&m->d_n_ids, 1);
   m->gemm_scratch_cap = (size_t)16 << 20;   // 64 MB: 176 CTAs x the largest partial tile (128 x 256 x 2 fp32)
   ok &= m->dalloc(&m->gemm_scratch, m->gemm_scratch_cap);
   m->attn_scratch_cap = (size_t)6 << 20;    // 24 MB: 176 CTAs x 64 rows x 260 fp32, with headroom
@@ -717,6 +723,14 @@ void plan_vision(Plan& pl) {
   e.out_rpo = m->nv * 256; e.out_obs_stride = m->P;
   pl.gemm("encoder_multi_modal_projector_w", nullptr, 0, m->vision_xn, Nv, 1152, 1152, e);
   pl.stage = 1;   // the prompt rows belong to the prefix stage (in multi-GPU latency mode the towers run elsewhere)
+  if (m->L > 0 && m->embed_table) {   // prompt given as token ids: embed on the device, inside the graph
+    const bf16* table = m->embed_table; const int vocab = m->vocab, L = m->L;
+    const int *ids = m->d_ids, *n_ids = m->d_n_ids; bf16* emb = m->lang; int* status = m->d_status;
+    pl.kernel([=](cudaStream_t st) {
+      return launch_ex(prompt_from_ids_kernel, dim3(L), dim3(256), 0, st, 1, pdl, table, vocab, ids, n_ids, emb,
+                       45.254833995939045f, status);
+    });
+  }
   if (m->L > 0) {  // pi0_infer.py:1344
     const bf16* emb = m->lang; float* x = m->encoder_x;
     const int L = m->L, P = m->P, off = m->nv * 256, B = m->B;
@@ -954,6 +968,33 @@ int vla_load_weight(vla_handle m, const char* key, const void* data, const int64
   if (!m) return VLA_ERR_STATE;
   if (!key || !shape) return m->fail(VLA_ERR_STATE, "null key or shape");
   cudaSetDevice(m->cfg.device);
+  if (!strcmp(key, "embedding_weight")) {
+    // token embedding table of the prompt (pi05_infer.py:726-743): kept as bf16 [vocab, 2048], used by
+    // vla_set_prompt_ids; must be loaded before vla_finalize so that the gather is part of the graph
+    if (m->finalized) return m->fail(VLA_ERR_STATE, "'embedding_weight' must be loaded before vla_finalize");
+    if (ndim != 2 || shape[1] != 2048 || shape[0] < 1 || shape[0] > (1 << 24))
+      return m->fail(VLA_ERR_SHAPE, "'embedding_weight' must be (vocab, 2048)");
+    if (dtype != VLA_BF16 && dtype != VLA_F32) return m->fail(VLA_ERR_SHAPE, "'%s': dtype must be bf16 or f32", key);
+    if (!data) return m->fail(VLA_ERR_STATE, "'%s': null data pointer", key);
+    const size_t count = (size_t)shape[0] * 2048;
+    if (m->embed_table) return m->fail(VLA_ERR_STATE, "'embedding_weight' is already loaded");
+    if (!m->dalloc(&m->embed_table, count)) return m->fail(VLA_ERR_CUDA, "allocation of the embedding table failed");
+    if (dtype == VLA_BF16) {
+      CK(cudaMemcpy(m->embed_table, data, count * 2, cudaMemcpyDefault));
+    } else {
+      float* raw = nullptr;
+      CK(cudaMalloc(&raw, count * 4));
+      cudaError_t ce = cudaMemcpy(raw, data, count * 4, cudaMemcpyDefault);
+      if (ce == cudaSuccess) {
+        f32_to_bf16_kernel<<<(unsigned)((count + 255) / 256), 256>>>(raw, m->embed_table, count);
+        ce = cudaDeviceSynchronize();
+      }
+      cudaFree(raw);
+      if (ce != cudaSuccess) return m->fail(VLA_ERR_CUDA, "embedding table upload: %s", cudaGetErrorString(ce));
+    }
+    m->vocab = (int)shape[0];
+    return VLA_OK;
+  }
   auto it = m->W.find(key);
   if (it == m->W.end()) return m->fail(VLA_ERR_KEY, "unknown checkpoint key '%s'", key);
   WEntry& e = it->second;
@@ -1033,7 +1074,21 @@ static int upload_scalars(vla_model* m) {
   const int valid = m->valid_len, pos_base = m->valid_len - 1;
   CK(cudaMemcpy(m->d_valid_len, &valid, sizeof(int), cudaMemcpyHostToDevice));
   CK(cudaMemcpy(m->d_pos_base, &pos_base, sizeof(int), cudaMemcpyHostToDevice));
+  CK(cudaMemcpy(m->d_n_ids, &m->n_ids, sizeof(int), cudaMemcpyHostToDevice));
   return VLA_OK;
+}
+
+int vla_set_prompt_ids(vla_handle m, const int32_t* ids, int len) {
+  if (!m) return VLA_ERR_STATE;
+  cudaSetDevice(m->cfg.device);
+  if (!m->embed_table) return m->fail(VLA_ERR_STATE, "vla_set_prompt_ids needs 'embedding_weight' loaded before vla_finalize");
+  if (len < 0 || len > m->L) return m->fail(VLA_ERR_SHAPE, "prompt of %d tokens does not fit the window of %d", len, m->L);
+  if (!m->pi05 && len != m->L) return m->fail(VLA_ERR_SHAPE, "Pi0 prompt length is fixed at %d", m->L);
+  if (len > 0 && !ids) return m->fail(VLA_ERR_STATE, "null token ids");
+  if (len > 0) CK(cudaMemcpy(m->d_ids, ids, (size_t)len * sizeof(int32_t), cudaMemcpyDefault));
+  m->n_ids = len;
+  m->valid_len = m->nv * 256 + len;
+  return upload_scalars(m);
 }
 
 int vla_set_prompt(vla_handle m, const void* embeds, int len) {
@@ -1043,6 +1098,7 @@ int vla_set_prompt(vla_handle m, const void* embeds, int len) {
   if (!m->pi05 && len != m->L) return m->fail(VLA_ERR_SHAPE, "Pi0 prompt length is fixed at %d", m->L);
   CK(cudaMemset(m->lang, 0, (size_t)std::max(m->L, 1) * 2048 * 2));
   if (len > 0) CK(cudaMemcpy(m->lang, embeds, (size_t)len * 2048 * 2, cudaMemcpyDefault));
+  m->n_ids = -1;     // the prompt rows are embeddings: the id gather inside the graph stays idle
   m->valid_len = m->nv * 256 + len;
   return upload_scalars(m);
 }

@@ -47,8 +47,10 @@ class Pi05Inference:
 
     With discrete_state_input=False the prompt is checkpoint['language_embeds'] and no tokenizer is touched.
     With discrete_state_input=True the prompt text "Task: ..., State: ...;\\nAction: " is tokenised on the
-    host, embedded with checkpoint['embedding_weight'] * sqrt(2048) and handed to the library per call; the
-    prompt window is max_prompt_len tokens and shorter prompts are masked by their valid length.
+    host and only the token ids go to the library: checkpoint['embedding_weight'] lives on the device and the
+    embedding (table[ids] * sqrt(2048), bf16) runs inside the captured graph.  The prompt window is
+    max_prompt_len tokens and shorter prompts are masked by their valid length.  Callers that tokenise
+    themselves pass forward(..., token_ids=ids) and may leave tokenizer_path=None.
     """
 
     def __init__(self, checkpoint, num_views, chunk_size, tokenizer_path=None, max_tokenize_len=200,
@@ -60,10 +62,12 @@ class Pi05Inference:
         self.num_views = num_views
         self.chunk_size = chunk_size
         self.max_tokenize_len = int(max_tokenize_len)
-        if discrete_state_input:
+        self.tokenizer = None
+        if discrete_state_input and tokenizer_path is not None:
             from transformers import AutoTokenizer
             self.tokenizer = AutoTokenizer.from_pretrained(tokenizer_path)
-            if max_prompt_text is not None and state_dim_for_max_prompt is not None:
+        if discrete_state_input:
+            if self.tokenizer is not None and max_prompt_text is not None and state_dim_for_max_prompt is not None:
                 self.max_prompt_len = self.estimate_max_prompt_len(self.tokenizer, max_prompt_text,
                                                                    int(state_dim_for_max_prompt),
                                                                    self.max_tokenize_len, 255)
@@ -75,20 +79,17 @@ class Pi05Inference:
             self.max_prompt_len = int(max_prompt_len)
         lang_rows = len(checkpoint["language_embeds"])
         shapes = pi05_shapes(lang_rows, n_vit_layers or 27, n_layers or 18)
-        self._engine = Engine(_capi.VLA_PI05, num_views, chunk_size, self.max_prompt_len, shapes, device=device,
-                              n_vit_layers=n_vit_layers, n_layers=n_layers, n_steps=n_steps, flags=flags)
-        for k, v in checkpoint.items():
-            if k != "embedding_weight":
-                self._engine.load(k, v)
-        self.prompt_embedding = None
-        self._prompt_embed_scale = None
         if discrete_state_input:
             if "embedding_weight" not in checkpoint:
                 raise KeyError("checkpoint must contain 'embedding_weight' when discrete_state_input=True")
-            emb_w = checkpoint["embedding_weight"]
-            emb_w = torch.from_numpy(emb_w) if isinstance(emb_w, np.ndarray) else emb_w
-            self.prompt_embedding = emb_w.to(device=self._engine.device, dtype=torch.bfloat16)
-            self._prompt_embed_scale = float(self.prompt_embedding.shape[1] ** 0.5)
+            shapes["embedding_weight"] = tuple(checkpoint["embedding_weight"].shape)
+        self._engine = Engine(_capi.VLA_PI05, num_views, chunk_size, self.max_prompt_len, shapes, device=device,
+                              n_vit_layers=n_vit_layers, n_layers=n_layers, n_steps=n_steps, flags=flags)
+        for k, v in checkpoint.items():
+            if k == "embedding_weight" and not discrete_state_input:
+                continue            # the reference skips the table in this mode (pi05_infer.py:666-668)
+            self._engine.load(k, torch.from_numpy(v) if isinstance(v, np.ndarray) else v)
+        self._prompt_embed_scale = float(2048 ** 0.5) if discrete_state_input else None
         self._language_embeds = checkpoint["language_embeds"]
         self.encoder_seq_len = num_views * 256 + self.max_prompt_len
         self._engine.finalize()
@@ -106,22 +107,33 @@ class Pi05Inference:
                         padding=False)["input_ids"][0]
         return int(ids.shape[0])
 
-    def build_prompt_embeds(self, task_prompt, state_tokens):
+    def build_prompt_ids(self, task_prompt, state_tokens):
+        """Token ids of the reference's prompt text (pi05_infer.py:769-783); the embedding happens on the device."""
+        if self.tokenizer is None:
+            raise RuntimeError("no tokenizer (tokenizer_path=None): pass token_ids to forward()")
         task_prompt = task_prompt.strip().replace("_", " ")
         state_str = " ".join(map(str, state_tokens.tolist()))
         full_prompt = f"Task: {task_prompt}, State: {state_str};\nAction: "
-        ids = self.tokenizer(full_prompt, return_tensors="pt", truncation=True, max_length=self.max_tokenize_len,
-                             padding=False)["input_ids"][0].to(self._engine.device)
-        embeds = self.prompt_embedding[ids] * self._prompt_embed_scale
+        return self.tokenizer(full_prompt, return_tensors="pt", truncation=True, max_length=self.max_tokenize_len,
+                              padding=False)["input_ids"][0]
+
+    def build_prompt_embeds(self, task_prompt, state_tokens):
+        """Same result as the reference's method (embeddings, length), computed on the host from the checkpoint
+        table; forward() does not use it."""
+        ids = self.build_prompt_ids(task_prompt, state_tokens)
+        table = self.checkpoint["embedding_weight"]
+        table = torch.from_numpy(table) if isinstance(table, np.ndarray) else table
+        embeds = table[ids.to(table.device)].to(torch.bfloat16) * self._prompt_embed_scale
         return embeds, int(embeds.shape[0])
 
     def forward(self, observation_images_normalized, diffusion_noise, task_prompt=None, state_tokens=None,
-                prompt_embeds=None):
+                prompt_embeds=None, token_ids=None):
         if prompt_embeds is not None:          # pre-embedded prompt (not in the reference)
             self._engine.set_prompt(prompt_embeds)
+        elif token_ids is not None:            # pre-tokenised prompt (not in the reference)
+            self._engine.set_prompt_ids(token_ids)
         elif self.discrete_state_input:
-            embeds, _ = self.build_prompt_embeds(task_prompt, state_tokens)
-            self._engine.set_prompt(embeds)
+            self._engine.set_prompt_ids(self.build_prompt_ids(task_prompt, state_tokens))
         self.buffers["observation_images_normalized"].copy_(observation_images_normalized)
         self.buffers["diffusion_noise"].copy_(diffusion_noise)
         self._engine.forward()

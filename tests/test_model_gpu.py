@@ -136,6 +136,49 @@ def test_pi05_small_valid_len():
     check_actions(out2, want2)
 
 
+def test_pi05_prompt_from_token_ids():
+    """discrete_state_input=True with pre-tokenised ids: the library embeds them on the device inside the graph
+    (pi05_infer.py:769-785, 811-822).  The gathered prompt rows must be bit-exact, the actions within tolerance."""
+    from pi05_infer import Pi05Inference
+    d = dev()
+    ck = synth.make_checkpoint("pi05", seed=1, prompt_ids=synth.prompt_ids(0, 3), n_vit_layers=2, n_layers=3)
+    g = torch.Generator().manual_seed(77)
+    vocab = 1000
+    ck["embedding_weight"] = (torch.randn(vocab, 2048, generator=g) * 0.02).to(torch.bfloat16)
+    images, _, noise = synth.make_inputs(1, 50, 1)
+    infer = Pi05Inference(ck, 1, 50, tokenizer_path=None, discrete_state_input=True, n_vit_layers=2, n_layers=3, n_steps=2,
+                          max_prompt_len=16)
+    w = {k: v.to(d).float() for k, v in ck.items() if k != "embedding_weight"}
+    vx = O.vision_encoder(w, images.to(d).float(), n_layers=2)
+    lang = infer._engine.buffer("language_embeds", (16, 2048))      # the bf16 prompt rows the gather writes
+    for n_ids, seed in ((11, 5), (16, 6), (3, 7)):      # a different prompt length per call
+        ids = torch.randint(0, vocab, (n_ids,), generator=torch.Generator().manual_seed(seed))
+        out = infer.forward(images, noise, token_ids=ids if seed != 6 else ids.to(d)).clone()   # host and device ids
+        torch.cuda.synchronize()
+        assert infer._engine.status_word() == 0
+        prompt = O.pi05_prompt_from_ids(ck["embedding_weight"], ids).to(d)
+        assert torch.equal(lang[:n_ids].float(), prompt), "gathered prompt rows differ"
+        assert not lang[n_ids:].any(), "rows beyond the prompt must be zero"
+        enc = torch.cat([O.project_vision(w, vx), prompt, torch.zeros(16 - n_ids, 2048, device=d)], 0)
+        K, V = O.prefix_encoder(w, enc, valid_len=256 + n_ids, n_layers=3)
+        want = O.pi05_decoder(w, K, V, noise.to(d).float(), 256 + n_ids, n_layers=3, n_steps=2)
+        check_actions(out, want)
+    # embeddings still work on the same object, and ids again after them
+    short = O.pi05_prompt_from_ids(ck["embedding_weight"], torch.arange(4)).to(torch.bfloat16)
+    out_e = infer.forward(images, noise, prompt_embeds=short).clone()
+    out_i = infer.forward(images, noise, token_ids=torch.arange(4)).clone()
+    torch.cuda.synchronize()
+    assert torch.equal(out_e, out_i)
+    # an id outside the table is clamped and reported through the status word, not a fault
+    infer.forward(images, noise, token_ids=torch.tensor([1, vocab + 5, 2]))
+    torch.cuda.synchronize()
+    assert infer._engine.status_word() != 0
+    with pytest.raises(RuntimeError):
+        infer.forward(images, noise, token_ids=torch.arange(17))      # longer than the prompt window
+    with pytest.raises(RuntimeError):
+        infer.forward(images, noise, task_prompt="pick", state_tokens=None)   # no tokenizer was given
+
+
 @pytest.mark.parametrize("cfg", [1, 2, 3])
 def test_full_configs(cfg):
     """Benchmark configurations 1-3 at full depth (27 / 18 layers, 10 steps)."""

@@ -80,3 +80,19 @@ def test_pi05_decoder_layer():
     close(v, g["V_new"], what="V_new")
     close(x, g["x_out"], what="x_out")
     assert g["probs"].float()[:, PV:PA].abs().max().item() == 0.0
+
+
+def test_prompt_from_ids_matches_embedding_module():
+    """The reference embeds prompt ids with nn.Embedding (bf16 table) and multiplies by the Python float
+    sqrt(2048) (pi05_infer.py:735-743, 783-785); the oracle's gather must give the same bf16 values."""
+    import torch
+    from oracle import vla_oracle as O
+    g = torch.Generator().manual_seed(3)
+    table = (torch.randn(300, 2048, generator=g) * 0.02).to(torch.bfloat16)
+    ids = torch.randint(0, 300, (23,), generator=g)
+    emb = torch.nn.Embedding(300, 2048, dtype=torch.bfloat16)
+    with torch.no_grad():
+        emb.weight.copy_(table)
+        want = emb(ids) * float(2048 ** 0.5)
+    assert want.dtype == torch.bfloat16
+    assert torch.equal(O.pi05_prompt_from_ids(table, ids), want.float())
