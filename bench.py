@@ -206,6 +206,69 @@ def expert_attention_timing(wl, device):
             "achieved": round(flops / (ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s", "ms_per_launch": round(ms, 5)}
 
 
+def preprocess_timing(wl, device):
+    """Camera frames -> model input on the device (vla_preprocess_image: Pillow-exact bilinear resize, pad,
+    normalise, bf16) for 640 x 480 frames, one per view: device time with the frames resident, end-to-end time from
+    pinned host frames, and the same work on the host cores (the oracle's numpy restatement, and Pillow itself,
+    which is what the reference's evaluation script calls)."""
+    from pi0_infer import Pi0Inference
+    from oracle import preproc_oracle as P
+    import numpy as np
+    nv = wl["num_views"]
+    infer = Pi0Inference({"language_embeds": torch.zeros(0, 2048)}, nv, wl["chunk"], n_vit_layers=1, n_layers=1, n_steps=1)
+    frames = [P.synthetic_frame(480, 640, 10 + v) for v in range(nv)]
+    dev_frames = [torch.from_numpy(f).to(device) for f in frames]
+    pin_frames = [torch.from_numpy(f).pin_memory() for f in frames]
+    eng = infer._engine
+
+    def run(fs):
+        for v, f in enumerate(fs):
+            eng.preprocess_image(v, f)
+    for _ in range(5):
+        run(dev_frames)
+    torch.cuda.synchronize()
+    iters = 200
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        run(dev_frames)
+    e1.record()
+    torch.cuda.synchronize()
+    dev_ms = e0.elapsed_time(e1) / iters
+    t0 = time.perf_counter()
+    for _ in range(iters):
+        run(pin_frames)
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / iters
+    t0 = time.perf_counter()
+    for f in frames:
+        P.normalize_image(P.resize_with_pad(f))
+    port_ms = (time.perf_counter() - t0) * 1e3
+    pil_ms = None
+    try:
+        from PIL import Image
+        t0 = time.perf_counter()
+        for _ in range(20):
+            for f in frames:
+                small = Image.fromarray(f).resize((224, 168), resample=Image.BILINEAR)
+                canvas = Image.new(small.mode, (224, 224), 0)
+                canvas.paste(small, (0, 28))
+                (np.array(canvas).astype(np.float32) / 255.0 * 2.0 - 1.0)
+        pil_ms = (time.perf_counter() - t0) * 1e3 / 20
+    except ImportError:
+        pass
+    # algorithmic bytes per frame: read the frame, write + read the horizontally resampled picture, write the bf16 view
+    per_frame = 480 * 640 * 3 + 2 * 480 * 224 * 3 + 224 * 224 * 3 * 2
+    pk, which = peaks()
+    gbs = nv * per_frame / (dev_ms * 1e-3) / 1e9
+    return {"kernel": "pp_resize_h_kernel + pp_resize_v_pad_norm_kernel, %d frames of 480x640" % nv, "bound": "hbm",
+            "achieved": round(gbs, 2), "peak": pk["hbm_gbs"], "peak_source": which, "unit": "GB/s", "frac": round(gbs / pk["hbm_gbs"], 5),
+            "ms_per_step": round(dev_ms, 5), "e2e_ms_per_step": round(e2e_ms, 5), "h2d_bytes_per_step": nv * 480 * 640 * 3,
+            "cpu_baseline": {"port_ms_per_step": round(port_ms, 3), "pillow_ms_per_step": None if pil_ms is None else round(pil_ms, 3),
+                             "cores": 1, "sample": "the same %d frames once (numpy restatement) / 20 times (Pillow)" % nv},
+            "note": "%d launches of ~1 MB each: bound by launch and memory latency, not by bandwidth" % (2 * nv)}
+
+
 def decoder_stream(wl, decoder_ms):
     """Action-expert weight streaming: algorithmic bytes of the 10 Euler steps (18 layers x 34.603 MB of weights
     + 2.23 MB of in/out projections + the K/V cache rows read by the suffix attention, per step) over the
@@ -363,10 +426,11 @@ def main():
                     help="replicas: every rank runs whole forwards (default); latency: one observation, one SigLIP tower "
                          "per rank + gather (needs at least num_views ranks)")
     ap.add_argument("--flags", type=int, default=0, help="vla_config.flags: 1 = no programmatic dependent launch, 2 = no CUDA graph")
-    ap.add_argument("--microbench", nargs="?", const="geglu", default=None, choices=["geglu", "expert_down", "expert_attention"],
+    ap.add_argument("--microbench", nargs="?", const="geglu", default=None, choices=["geglu", "expert_down", "expert_attention", "preprocess"],
                     help="time one kernel alone and print its roofline object: geglu = the dominant kernel of the workload "
                          "(prefix GeGLU GEMM); expert_down = action-expert down projection (51 x 4096 -> 1024, HBM-bound weight "
-                         "stream); expert_attention = suffix attention of the action expert on the tcgen05 kernel")
+                         "stream); expert_attention = suffix attention of the action expert on the tcgen05 kernel; preprocess = camera "
+                         "frames -> model input (resize, pad, normalise) on the device against the host code")
     ap.add_argument("--profile-forward", action="store_true",
                     help="run two forwards and bracket the second with cudaProfilerStart/Stop (for ncu "
                          "--profile-from-start off); prints no benchmark line")
@@ -385,7 +449,8 @@ def main():
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if args.microbench:
-        fn = {"geglu": dominant_kernel_roofline, "expert_down": expert_down_roofline, "expert_attention": expert_attention_timing}
+        fn = {"geglu": dominant_kernel_roofline, "expert_down": expert_down_roofline, "expert_attention": expert_attention_timing,
+              "preprocess": preprocess_timing}
         print(json.dumps(fn[args.microbench](wl, device)), flush=True)
         return
     dist = None

@@ -103,6 +103,32 @@ int vla_forward_stages(vla_handle h, int stage_mask, void* stream);
  * actions out and synchronises.  `state` is ignored for Pi05 (may be NULL). */
 int vla_forward_host(vla_handle h, const void* images, const void* state, const void* noise, void* actions_out);
 
+/* ---- the steps either side of the forward in a robot loop -----------------------------------------------
+ * The reference does these on the host with PIL and numpy in its evaluation script (test.py:82-151, 180-204);
+ * here they run on the device and give bit-identical results. */
+
+/* Camera frame -> model input (test.py:99-116, 157-162): `frame` is uint8 (height, width, 3) RGB in host or device
+ * memory.  Resized keeping the aspect ratio with Pillow's BILINEAR resample (Image.resize), pasted centred on a
+ * black 224 x 224 canvas, scaled to x / 255 * 2 - 1 and stored as bf16 into view `view` of observation `obs` of
+ * "observation_images_normalized".  A 224 x 224 frame is only scaled.  Asynchronous on `stream`. */
+int vla_preprocess_image(vla_handle h, int obs, int view, const uint8_t* frame, int height, int width, void* stream);
+
+/* Robot state -> model input (test.py:118-131), float64: mode 0 (Pi0) (state - a) / (b + 1e-6) with a = mean,
+ * b = std; mode 1 (Pi05) (state - a) / (b - a + 1e-6) * 2 - 1 with a = q01, b = q99.  n <= 32 host values each.
+ * For Pi0 the result is rounded to float32 then bf16 and zero-padded into "observation_state_normalized" of
+ * observation `obs`; when normalized_out is not NULL the n float64 values are also returned (Pi05 digitises them
+ * into prompt tokens on the host, test.py:136-137) and the call synchronises `stream`. */
+int vla_preprocess_state(vla_handle h, int obs, const double* state, const double* a, const double* b, int n, int mode,
+                         double* normalized_out, void* stream);
+
+/* Action chunk -> robot command (test.py:139-151, 196-200), float64: the bf16 actions of observation `obs` are
+ * un-normalised (mode 0: x * (b + 1e-6) + a with a = mean, b = std; mode 1: (x + 1) / 2 * (b - a + 1e-6) + a with
+ * a = q01, b = q99; statistics beyond n_stats count as zero), cut to action_dim columns, and the raw state is added
+ * (delta -> absolute) except to the last dimension of every 7-wide arm.  `out` (chunk, action_dim) float64, host
+ * or device; the call synchronises `stream`. */
+int vla_postprocess_actions(vla_handle h, int obs, const double* a, const double* b, int n_stats, int mode,
+                            const double* state_raw, int n_state, int action_dim, double* out, void* stream);
+
 /* Device status word: OR of bounded-wait timeouts / shape violations seen by any kernel (0 = clean). */
 int vla_status_word(vla_handle h, int* out);
 

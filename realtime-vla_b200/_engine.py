@@ -3,6 +3,8 @@ buffers as torch tensors without copying, and mirrors the checkpoint-loading sem
 constructors (pi0_infer.py:1337-1338, pi05_infer.py:666-668)."""
 import ctypes as C
 
+import numpy as np
+
 import torch
 
 import _capi
@@ -60,6 +62,7 @@ class Engine:
         self.handle = h
         self.shapes = shapes
         self.batch = batch
+        self.chunk_size = chunk_size
 
     def close(self):
         if getattr(self, "handle", None):
@@ -111,6 +114,48 @@ class Engine:
         """Prompt as token ids (int, host or device): embedded on the device from 'embedding_weight', inside the graph."""
         ids = torch.as_tensor(ids).detach().to(torch.int32).contiguous()
         _capi.check(self.lib.vla_set_prompt_ids(self.handle, C.c_void_p(ids.data_ptr()), int(ids.numel())), self.handle)
+
+    # ---- the steps either side of the forward (the reference's evaluation script does them with PIL / numpy) ----
+    def preprocess_image(self, view, frame, obs=0):
+        """uint8 (H, W, 3) RGB frame (numpy array or tensor, host or device) -> resized, padded, normalised view."""
+        t = frame if isinstance(frame, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(frame))
+        if t.dtype != torch.uint8 or t.dim() != 3 or t.shape[2] != 3:
+            raise RuntimeError("camera frame must be uint8 (H, W, 3), got %s %s" % (t.dtype, tuple(t.shape)))
+        t = t.contiguous()
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _capi.check(self.lib.vla_preprocess_image(self.handle, obs, view, C.c_void_p(t.data_ptr()), t.shape[0], t.shape[1],
+                                                  C.c_void_p(stream)), self.handle)
+        if not t.is_cuda:
+            torch.cuda.current_stream(self.device).synchronize()   # the host frame may be released after the call
+
+    @staticmethod
+    def _f64(x, n=None):
+        a = np.ascontiguousarray(np.asarray(x, dtype=np.float64).reshape(-1))
+        return a, a.ctypes.data_as(C.POINTER(C.c_double))
+
+    def preprocess_state(self, state, a, b, mode, obs=0, want_values=False):
+        """mode 0: (state - mean) / (std + 1e-6); mode 1: (state - q01) / (q99 - q01 + 1e-6) * 2 - 1; float64."""
+        s, ps = self._f64(state)
+        n = s.shape[0]
+        (av, pa), (bv, pb) = self._f64(np.asarray(a)[:n]), self._f64(np.asarray(b)[:n])
+        if av.shape[0] != n or bv.shape[0] != n:
+            raise RuntimeError("statistics shorter than the state")
+        out = np.empty(n, np.float64) if want_values else None
+        po = out.ctypes.data_as(C.POINTER(C.c_double)) if want_values else None
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _capi.check(self.lib.vla_preprocess_state(self.handle, obs, ps, pa, pb, n, mode, po, C.c_void_p(stream)), self.handle)
+        return out
+
+    def postprocess_actions(self, a, b, mode, state_raw, action_dim, obs=0):
+        """-> float64 (chunk, action_dim): un-normalised actions, delta -> absolute except the gripper dimensions."""
+        (av, pa), (bv, pb) = self._f64(a), self._f64(b)
+        sv, ps = self._f64(state_raw)
+        out = np.empty((self.chunk_size, action_dim), np.float64)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _capi.check(self.lib.vla_postprocess_actions(self.handle, obs, pa, pb, min(av.shape[0], bv.shape[0]), mode, ps, sv.shape[0],
+                                                     action_dim, out.ctypes.data_as(C.POINTER(C.c_double)), C.c_void_p(stream)),
+                    self.handle)
+        return out
 
     def forward(self):
         stream = torch.cuda.current_stream(self.device).cuda_stream

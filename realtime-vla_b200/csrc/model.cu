@@ -21,6 +21,7 @@
 #include "attention_tc.cuh"
 #include "elementwise.cuh"
 #include "gemm_sm100.cuh"
+#include "preprocess.cuh"
 
 namespace {
 
@@ -420,6 +421,13 @@ struct vla_model {
   int vocab = 0;
   int *d_ids = nullptr, *d_n_ids = nullptr;   // prompt token ids and their count (-1: prompt given as embeddings)
   int n_ids = -1;
+  // pre/post-processing: resample tables per (input size, output size), frame staging that grows on demand
+  struct ResampleTable { int ksize; int* bounds; int* kk; };
+  std::map<std::pair<int, int>, ResampleTable> resample;
+  uint8_t* pp_frame = nullptr;   // staged camera frame followed by the horizontally resampled picture
+  size_t pp_frame_cap = 0;
+  double* pp_vec = nullptr;      // [256] small float64 vectors (state, statistics)
+  double* pp_out = nullptr;      // [chunk * 32] un-normalised actions
   float* gemm_scratch;            // split-K partial tiles of whichever GEMM is running (kernels never overlap)
   size_t gemm_scratch_cap = 0;    // floats
   float* attn_scratch;            // key-split partial outputs of whichever attention kernel is running
@@ -1217,6 +1225,158 @@ int vla_forward_host(vla_handle m, const void* images, const void* state, const 
   int rc = vla_forward(m, st);
   if (rc) return rc;
   CK(cudaMemcpyAsync(actions_out, m->noise, B * m->C * 32 * 2, cudaMemcpyDeviceToHost, st));
+  CK(cudaStreamSynchronize(st));
+  return VLA_OK;
+}
+
+// Pillow's precompute_coeffs + normalize_coeffs_8bpc for the BILINEAR filter over a whole axis, in the same
+// double arithmetic (src/libImaging/Resample.c of Pillow; the reference resizes with Image.resize(..., BILINEAR),
+// test.py:107).  Tables are built once per (input size, output size) and kept on the device.
+static int resample_table(vla_model* m, int in_size, int out_size, vla_model::ResampleTable* out) {
+  auto key = std::make_pair(in_size, out_size);
+  auto it = m->resample.find(key);
+  if (it != m->resample.end()) { *out = it->second; return VLA_OK; }
+  const double scale = (double)in_size / (double)out_size;
+  const double filterscale = scale < 1.0 ? 1.0 : scale;
+  const double support = 1.0 * filterscale;
+  const int ksize = (int)std::ceil(support) * 2 + 1;
+  std::vector<int> bounds((size_t)out_size * 2), kk((size_t)out_size * ksize, 0);
+  std::vector<double> w(ksize);
+  const double ss = 1.0 / filterscale;
+  for (int xx = 0; xx < out_size; ++xx) {
+    const double center = (xx + 0.5) * scale;
+    int xmin = (int)(center - support + 0.5);
+    if (xmin < 0) xmin = 0;
+    int xmax = (int)(center + support + 0.5);
+    if (xmax > in_size) xmax = in_size;
+    xmax -= xmin;
+    double ww = 0.0;
+    for (int x = 0; x < ksize; ++x) w[x] = 0.0;
+    for (int x = 0; x < xmax; ++x) {
+      double a = (x + xmin - center + 0.5) * ss;
+      if (a < 0.0) a = -a;
+      w[x] = a < 1.0 ? 1.0 - a : 0.0;
+      ww += w[x];
+    }
+    for (int x = 0; x < xmax; ++x)
+      if (ww != 0.0) w[x] /= ww;
+    for (int x = 0; x < ksize; ++x)
+      kk[(size_t)xx * ksize + x] = w[x] < 0 ? (int)(-0.5 + w[x] * (1 << PP_PRECISION_BITS)) : (int)(0.5 + w[x] * (1 << PP_PRECISION_BITS));
+    bounds[2 * xx] = xmin;
+    bounds[2 * xx + 1] = xmax;
+  }
+  vla_model::ResampleTable t{ksize, nullptr, nullptr};
+  if (!m->dalloc(&t.bounds, bounds.size()) || !m->dalloc(&t.kk, kk.size())) return m->fail(VLA_ERR_CUDA, "allocation failed");
+  CK(cudaMemcpy(t.bounds, bounds.data(), bounds.size() * sizeof(int), cudaMemcpyHostToDevice));
+  CK(cudaMemcpy(t.kk, kk.data(), kk.size() * sizeof(int), cudaMemcpyHostToDevice));
+  m->resample[key] = t;
+  *out = t;
+  return VLA_OK;
+}
+
+int vla_preprocess_image(vla_handle m, int obs, int view, const uint8_t* frame, int height, int width, void* stream) {
+  if (!m || !m->finalized) return VLA_ERR_STATE;
+  cudaSetDevice(m->cfg.device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (obs < 0 || obs >= m->B || view < 0 || view >= m->nv) return m->fail(VLA_ERR_SHAPE, "observation %d / view %d out of range", obs, view);
+  if (!frame || height < 1 || width < 1 || height > 8192 || width > 8192) return m->fail(VLA_ERR_SHAPE, "frame must be (1..8192, 1..8192, 3) uint8");
+  // sizes and paste offsets exactly as the host code computes them (test.py:99-113); a 224 x 224 frame passes through
+  int rh = 224, rw = 224, pad_h = 0, pad_w = 0;
+  if (!(width == 224 && height == 224)) {
+    const double ratio = std::max((double)width / 224.0, (double)height / 224.0);
+    rh = (int)((double)height / ratio);
+    rw = (int)((double)width / ratio);
+    pad_h = std::max(0, (int)((224 - rh) / 2.0));
+    pad_w = std::max(0, (int)((224 - rw) / 2.0));
+  }
+  if (rh < 1 || rw < 1) return m->fail(VLA_ERR_SHAPE, "frame of %d x %d is too elongated to resize to 224 x 224", height, width);
+  const size_t frame_bytes = (size_t)height * width * 3, tmp_bytes = (size_t)height * rw * 3;
+  const size_t need = ((frame_bytes + 255) & ~(size_t)255) + tmp_bytes;
+  if (need > m->pp_frame_cap) {   // grows only when a larger camera format shows up
+    CK(cudaStreamSynchronize(st));
+    uint8_t* q = nullptr;
+    CK(cudaMalloc(&q, need));
+    if (m->pp_frame) {
+      for (auto& a : m->allocs)
+        if (a == m->pp_frame) a = q;
+      cudaFree(m->pp_frame);
+    } else {
+      m->allocs.push_back(q);
+    }
+    m->bytes += need - m->pp_frame_cap;
+    m->pp_frame = q;
+    m->pp_frame_cap = need;
+  }
+  vla_model::ResampleTable th, tv;
+  int rc = resample_table(m, width, rw, &th);
+  if (rc) return rc;
+  rc = resample_table(m, height, rh, &tv);
+  if (rc) return rc;
+  uint8_t* tmp = m->pp_frame + ((frame_bytes + 255) & ~(size_t)255);
+  // a frame that already lives on this GPU is read in place; anything else is staged first
+  const uint8_t* src = frame;
+  cudaPointerAttributes at;
+  const bool on_device = cudaPointerGetAttributes(&at, frame) == cudaSuccess && at.type == cudaMemoryTypeDevice && at.device == m->cfg.device;
+  (void)cudaGetLastError();   // an unregistered host pointer is not an error here
+  if (!on_device) {
+    CK(cudaMemcpyAsync(m->pp_frame, frame, frame_bytes, cudaMemcpyDefault, st));
+    src = m->pp_frame;
+  }
+  pp_resize_h_kernel<<<(unsigned)((height * rw + 255) / 256), 256, 0, st>>>(src, height, width, tmp, rw, th.bounds, th.kk, th.ksize);
+  bf16* dst = m->images + ((size_t)obs * m->nv + view) * 224 * 224 * 3;
+  pp_resize_v_pad_norm_kernel<<<(224 * 224 + 255) / 256, 256, 0, st>>>(tmp, height, rw, rh, pad_h, pad_w, tv.bounds, tv.kk, tv.ksize, dst);
+  CK(cudaGetLastError());
+  return VLA_OK;
+}
+
+static int pp_small_buffers(vla_model* m) {
+  if (!m->pp_vec && !m->dalloc(&m->pp_vec, 256)) return m->fail(VLA_ERR_CUDA, "allocation failed");
+  if (!m->pp_out && !m->dalloc(&m->pp_out, (size_t)m->C * 32)) return m->fail(VLA_ERR_CUDA, "allocation failed");
+  return VLA_OK;
+}
+
+int vla_preprocess_state(vla_handle m, int obs, const double* state, const double* a, const double* b, int n, int mode,
+                         double* normalized_out, void* stream) {
+  if (!m || !m->finalized) return VLA_ERR_STATE;
+  cudaSetDevice(m->cfg.device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (obs < 0 || obs >= m->B || n < 1 || n > 32 || !state || !a || !b || (mode != 0 && mode != 1))
+    return m->fail(VLA_ERR_SHAPE, "state: 1..32 values with two statistics vectors, mode 0 or 1");
+  int rc = pp_small_buffers(m);
+  if (rc) return rc;
+  double host[96];
+  for (int i = 0; i < n; ++i) { host[i] = state[i]; host[n + i] = a[i]; host[2 * n + i] = b[i]; }
+  CK(cudaMemcpyAsync(m->pp_vec, host, (size_t)3 * n * sizeof(double), cudaMemcpyHostToDevice, st));
+  // Pi05 has no state input buffer (its state goes into the prompt as tokens): only the float64 values come back
+  bf16* dst = m->pi05 ? nullptr : m->state + (size_t)obs * 32;
+  pp_state_kernel<<<1, 32, 0, st>>>(m->pp_vec, n, mode, dst, m->pp_vec + 128);
+  CK(cudaGetLastError());
+  if (normalized_out) {
+    CK(cudaMemcpyAsync(normalized_out, m->pp_vec + 128, (size_t)n * sizeof(double), cudaMemcpyDefault, st));
+    CK(cudaStreamSynchronize(st));
+  }
+  return VLA_OK;
+}
+
+int vla_postprocess_actions(vla_handle m, int obs, const double* a, const double* b, int n_stats, int mode,
+                            const double* state_raw, int n_state, int action_dim, double* out, void* stream) {
+  if (!m || !m->finalized) return VLA_ERR_STATE;
+  cudaSetDevice(m->cfg.device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (obs < 0 || obs >= m->B || n_stats < 1 || n_stats > 32 || action_dim < 1 || action_dim > 32 || n_state < action_dim ||
+      n_state > 32 || !a || !b || !state_raw || !out || (mode != 0 && mode != 1))
+    return m->fail(VLA_ERR_SHAPE, "actions: 1..32 statistics, action_dim <= state length <= 32, mode 0 or 1");
+  int rc = pp_small_buffers(m);
+  if (rc) return rc;
+  double host[96];
+  for (int i = 0; i < n_stats; ++i) { host[i] = a[i]; host[n_stats + i] = b[i]; }
+  for (int i = 0; i < n_state; ++i) host[2 * n_stats + i] = state_raw[i];
+  CK(cudaMemcpyAsync(m->pp_vec, host, (size_t)(2 * n_stats + n_state) * sizeof(double), cudaMemcpyHostToDevice, st));
+  const int total = m->C * action_dim;
+  pp_actions_kernel<<<(total + 127) / 128, 128, 0, st>>>(m->noise + (size_t)obs * m->C * 32, m->C, m->pp_vec, n_stats, n_state, mode,
+                                                          action_dim, m->pp_out);
+  CK(cudaGetLastError());
+  CK(cudaMemcpyAsync(out, m->pp_out, (size_t)total * sizeof(double), cudaMemcpyDefault, st));
   CK(cudaStreamSynchronize(st));
   return VLA_OK;
 }
