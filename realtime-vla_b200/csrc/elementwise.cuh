@@ -157,6 +157,15 @@ __global__ void prompt_from_ids_kernel(const bf16* __restrict__ table, int vocab
   const bf16* src = table + (size_t)id * 2048;
   for (int c = threadIdx.x; c < 2048; c += blockDim.x) dst[c] = __float2bfloat16(__bfloat162float(src[c]) * scale);
 }
+// adaRMS shift rows as a bf16 GEMM operand: style [step][layer][3072] fp32 = [scale | shift | gate] ->
+// out [layer][step][1024] bf16 (the shift third), so that shift @ W can be precomputed per (step, layer).
+__global__ void style_shift_rows_kernel(const float* __restrict__ style, int n_layers, int n_steps, bf16* __restrict__ out) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)n_layers * n_steps * 1024) return;
+  const int c = (int)(idx & 1023);
+  const int step = (int)((idx >> 10) % n_steps), l = (int)((idx >> 10) / n_steps);
+  out[idx] = __float2bfloat16(style[((size_t)step * n_layers + l) * 3072 + 1024 + c]);
+}
 // dst rows (b*dst_stride + dst_off) <- src rows b, fp32, `width` columns
 __global__ void copy_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, int width, int dst_stride_rows,
                                  int dst_off_rows, int batch) {

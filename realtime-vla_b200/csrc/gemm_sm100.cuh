@@ -36,6 +36,10 @@ struct GemmEpi {
   const float* gate;
   bf16* mirror;  // optional bf16 copy of the value written to outf
   int ld_mirror;
+  const float* mirror_scale;  // optional [features]: the mirror holds value * (1 + mirror_scale[n]) (adaRMS scale of the
+                              // norm that consumes it, pi05_infer.py:78-113: y = rms(x) * (1 + scale) + shift)
+  const float* bias2;         // optional bias of the second accumulator (GeGLU "up"); with ssq_in both biases are
+                              // added after the per-token scale, i.e. they carry shift @ W of a folded adaRMS norm
   int out_rpo;         // > 0: token t is written to row (t / out_rpo) * out_obs_stride + t % out_rpo
   int out_obs_stride;
   // RMS norm folded into the GEMMs around a residual stream (the normalisation has no learned scale, so
@@ -128,6 +132,7 @@ struct EpiThread {
   int n;
   bool n_ok;
   float bias, gate;
+  float bias2, mscale;
   int pos_base;
 };
 
@@ -144,7 +149,7 @@ __device__ __forceinline__ void gemm_epilogue_cols(const GemmEpi& e, const EpiTh
     float x[NC];
     if (e.act == ACT_GEGLU) {
 #pragma unroll
-      for (int j = 0; j < NC; ++j) x[j] = gelu_tanh_f(v[j] + th.bias) * v2[j];
+      for (int j = 0; j < NC; ++j) x[j] = gelu_tanh_f(v[j] + th.bias) * (v2[j] + th.bias2);
     } else if (e.act == ACT_GELU) {
 #pragma unroll
       for (int j = 0; j < NC; ++j) x[j] = gelu_tanh_f(v[j] + th.bias);
@@ -195,7 +200,7 @@ __device__ __forceinline__ void gemm_epilogue_cols(const GemmEpi& e, const EpiTh
     for (int j = 0; j < NC; ++j) {
       if (j < n_valid && th.n_ok) {
         e.outf[orow[j] * e.ld_outf + n] = r[j];
-        if (e.mirror) e.mirror[orow[j] * e.ld_mirror + n] = __float2bfloat16(r[j]);
+        if (e.mirror) e.mirror[orow[j] * e.ld_mirror + n] = __float2bfloat16(r[j] * th.mscale);
       }
     }
     if (e.ssq_out) {   // per-token sum of squares over this warp's 32 features (warp-collective: no early exit above)
@@ -232,8 +237,9 @@ __device__ __forceinline__ void gemm_epilogue_cols(const GemmEpi& e, const EpiTh
     float x[NC];
 #pragma unroll
     for (int j = 0; j < NC; ++j) {
-      const float partner = __shfl_xor_sync(0xffffffffu, v[j], 1);
-      x[j] = v[j] * c[j] + sgn * partner * s[j];
+      const float val = v[j] + th.bias;
+      const float partner = __shfl_xor_sync(0xffffffffu, val, 1);
+      x[j] = val * c[j] + sgn * partner * s[j];
     }
 #pragma unroll
     for (int j = 0; j < NC; ++j) {
@@ -407,12 +413,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   th_first.bias = (is_epi && n_ok && p.epi.bias) ? p.epi.bias[n] : 0.f;
   th_first.gate = (is_epi && n_ok && p.epi.gate) ? p.epi.gate[n] : 1.f;
   th_first.pos_base = (p.epi.kind == EPI_QKV && p.epi.pos_base) ? *p.epi.pos_base : 0;
+  th_first.bias2 = (is_epi && n_ok && p.epi.bias2) ? p.epi.bias2[n] : 0.f;
+  th_first.mscale = (is_epi && n_ok && p.epi.mirror_scale) ? 1.f + p.epi.mirror_scale[n] : 1.f;
   EpiThread th2 = th_first;   // second feature tile of an m256 launch
   if (m256) {
     th2.n = n + 128;
     th2.n_ok = th2.n < p.n_feat;
     th2.bias = (is_epi && th2.n_ok && p.epi.bias) ? p.epi.bias[th2.n] : 0.f;
     th2.gate = (is_epi && th2.n_ok && p.epi.gate) ? p.epi.gate[th2.n] : 1.f;
+    th2.mscale = (is_epi && th2.n_ok && p.epi.mirror_scale) ? 1.f + p.epi.mirror_scale[th2.n] : 1.f;
   }
   const int n_pass = m256 ? 2 : 1;
   bool acc_ok = false;
@@ -462,7 +471,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         if (p.epi.kind == EPI_BF16) {
           if (p.epi.act == ACT_GEGLU) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) x[j] = gelu_tanh_f(__uint_as_float(v[j]) + th.bias) * __uint_as_float(v2[j]);
+            for (int j = 0; j < 32; ++j) x[j] = gelu_tanh_f(__uint_as_float(v[j]) + th.bias) * (__uint_as_float(v2[j]) + th.bias2);
           } else if (p.epi.act == ACT_GELU) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) x[j] = gelu_tanh_f(__uint_as_float(v[j]) + th.bias);
@@ -487,7 +496,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           }
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const float val = __uint_as_float(v[j]);
+            const float val = __uint_as_float(v[j]) + th.bias;
             const float partner = __shfl_xor_sync(0xffffffffu, val, 1);
             x[j] = val * cs[j] + sgn * partner * sn[j];
           }

@@ -415,6 +415,9 @@ struct vla_model {
   bf16* lang;
   float *rope_cos, *rope_sin;
   float *style_attn, *style_ffn, *style_fin;
+  // folded adaRMS (Pi05 expert): shift rows as bf16 GEMM operands and shift @ W per (step, layer)
+  bf16 *shift_attn_bf = nullptr, *shift_ffn_bf = nullptr;          // [layer][step][1024]
+  float *sw_qkv = nullptr, *sw_gate = nullptr, *sw_up = nullptr;   // [step][layer][2560 | 4096 | 4096]
   bf16 *time_tmp, *time_emb;
   int *d_valid_len, *d_pos_base, *d_status;
   bf16* embed_table = nullptr;    // optional token embedding table [vocab, 2048] ('embedding_weight')
@@ -603,6 +606,11 @@ bool alloc_buffers(vla_model* m) {
     ok &= m->dalloc(&m->style_attn, (size_t)m->nsteps * m->nl * 3072);
     ok &= m->dalloc(&m->style_ffn, (size_t)m->nsteps * m->nl * 3072);
     ok &= m->dalloc(&m->style_fin, (size_t)m->nsteps * 3072);
+    ok &= m->dalloc(&m->shift_attn_bf, (size_t)m->nl * m->nsteps * 1024);
+    ok &= m->dalloc(&m->shift_ffn_bf, (size_t)m->nl * m->nsteps * 1024);
+    ok &= m->dalloc(&m->sw_qkv, (size_t)m->nsteps * m->nl * 2560);
+    ok &= m->dalloc(&m->sw_gate, (size_t)m->nsteps * m->nl * 4096);
+    ok &= m->dalloc(&m->sw_up, (size_t)m->nsteps * m->nl * 4096);
     ok &= m->dalloc(&m->time_tmp, (size_t)10 * 1024);
     ok &= m->dalloc(&m->time_emb, (size_t)10 * 1024);
   }
@@ -826,17 +834,22 @@ void plan_decoder(Plan& pl) {
       bf16* vt = m->vtcache + (size_t)l * B * 256 * m->T_pad;
       const float* st_attn = pi05 ? m->style_attn + ((size_t)step * m->nl + l) * 3072 : nullptr;
       const float* st_ffn = pi05 ? m->style_ffn + ((size_t)step * m->nl + l) * 3072 : nullptr;
-      // Pi0: the scale-free RMS norms are folded into the GEMMs (f * (x @ W)); only the first layer of a step
-      // normalises explicitly, because its input comes from the action MLP.  Pi05 (adaRMS) keeps the norm kernels.
-      const bool fold = !pi05;
-      const bool explicit_norm = !fold || l == 0;
+      // The RMS norms are folded into the GEMMs (f * (x @ W)); only the first layer of a step normalises
+      // explicitly, because its input comes from the action MLP.  Pi05 (adaRMS): the producer's bf16 mirror holds
+      // x * (1 + scale) of the norm that consumes it and the consumer adds the precomputed shift @ W as a bias.
+      const bool fold = true;
+      const bool explicit_norm = l == 0;
+      const size_t sl = (size_t)step * m->nl + l;
       if (explicit_norm) pl.norm(m->decoder_x, m->decoder_xn, Ns, 1024, pi05 ? NORM_ADARMS : NORM_RMS, st_attn, nullptr);
       GemmEpi e = pl.epi0();
       e.kind = EPI_QKV; e.q = m->decoder_q; e.kc = kc; e.vc = vc; e.rope_cos = m->rope_cos; e.rope_sin = m->rope_sin;
       e.pos_off = pi05 ? 0 : m->P; e.pos_base = pi05 ? m->d_pos_base : nullptr;
       e.rows_per_obs = S; e.kv_obs_stride = m->T; e.kv_row_off = m->P;
       e.vt = vt; e.vt_ld = m->T_pad;
-      if (!explicit_norm) { e.ssq_in = m->decoder_ssq; e.ssq_ld = Ns; e.ssq_slots = 32; e.ssq_inv_d = 1.0f / 1024.0f; }
+      if (!explicit_norm) {
+        e.ssq_in = m->decoder_ssq; e.ssq_ld = Ns; e.ssq_slots = 32; e.ssq_inv_d = 1.0f / 1024.0f;
+        if (pi05) e.bias = m->sw_qkv + sl * 2560;
+      }
       pl.gemm("decoder_attn_qkv_w", nullptr, l, explicit_norm ? m->decoder_xn : m->decoder_xb, Ns, 1024, 1024, e);
       AttnParams a; memset(&a, 0, sizeof a);
       a.q = m->decoder_q; a.k = kc; a.v = vc; a.o = m->decoder_attn;
@@ -852,16 +865,18 @@ void plan_decoder(Plan& pl) {
       e.kind = EPI_RESID; e.outf = m->decoder_x; e.ld_outf = 1024; e.res_in = m->decoder_x; e.ld_res = 1024;
       e.gate = pi05 ? st_attn + 2048 : nullptr;
       if (fold) { e.mirror = m->decoder_xb; e.ld_mirror = 1024; e.ssq_out = m->decoder_ssq; e.ssq_ld = Ns; }
+      if (pi05) e.mirror_scale = st_ffn;   // scale third of the pre-MLP norm's style row
       pl.gemm("decoder_attn_o_w", nullptr, l, m->decoder_attn, Ns, 2048, 2048, e);
-      if (!fold) pl.norm(m->decoder_x, m->decoder_xn, Ns, 1024, NORM_ADARMS, st_ffn, nullptr);
       e = pl.epi0();
       e.kind = EPI_BF16; e.act = ACT_GEGLU; e.out = m->decoder_hidden; e.ld_out = 4096;
       if (fold) { e.ssq_in = m->decoder_ssq; e.ssq_ld = Ns; e.ssq_slots = 32; e.ssq_inv_d = 1.0f / 1024.0f; }
+      if (pi05) { e.bias = m->sw_gate + sl * 4096; e.bias2 = m->sw_up + sl * 4096; }
       pl.gemm("decoder_ffn_gate_w", "decoder_ffn_up_w", l, fold ? m->decoder_xb : m->decoder_xn, Ns, 1024, 1024, e);
       e = pl.epi0();
       e.kind = EPI_RESID; e.outf = m->decoder_x; e.ld_outf = 1024; e.res_in = m->decoder_x; e.ld_res = 1024;
       e.gate = pi05 ? st_ffn + 2048 : nullptr;
       if (fold) { e.mirror = m->decoder_xb; e.ld_mirror = 1024; e.ssq_out = m->decoder_ssq; e.ssq_ld = Ns; }
+      if (pi05 && l + 1 < m->nl) e.mirror_scale = st_attn + 3072;   // pre-attention norm of the next layer, same step
       pl.gemm("decoder_ffn_down_w", nullptr, l, m->decoder_hidden, Ns, 4096, 4096, e);
     }
     // Euler update: noise += norm(x_action) @ W_out + b_out   (pi0_infer.py:1224-1230, pi05_infer.py:511-523)
@@ -907,6 +922,26 @@ int pi05_precompute(vla_model* m, cudaStream_t st) {
   GemmEpi s = pl.epi0();
   s.kind = EPI_RESID; s.bias = pl.vec("decoder_final_norm_mod_b"); s.outf = m->style_fin; s.ld_outf = 3072;
   pl.gemm("decoder_final_norm_mod_w", nullptr, 0, m->time_emb, ns, 1024, 1024, s);
+  // The adaRMS norms of the expert are folded into the GEMMs that consume them:
+  //   (rms(x) * (1 + scale) + shift) @ W = f * ((x * (1 + scale)) @ W) + shift @ W,  f = rsqrt(mean(x^2) + eps),
+  // so shift @ W is computed here once per (step, layer) and enters the GEMM epilogues as a bias.
+  {
+    const int nl = m->nl;
+    const unsigned blocks = (unsigned)(((size_t)nl * ns * 1024 + 255) / 256);
+    const float *sa = m->style_attn, *sf = m->style_ffn;
+    bf16 *oa = m->shift_attn_bf, *of = m->shift_ffn_bf;
+    pl.kernel([=](cudaStream_t st2) { style_shift_rows_kernel<<<blocks, 256, 0, st2>>>(sa, nl, ns, oa); return cudaGetLastError(); });
+    pl.kernel([=](cudaStream_t st2) { style_shift_rows_kernel<<<blocks, 256, 0, st2>>>(sf, nl, ns, of); return cudaGetLastError(); });
+    for (int l = 0; l < nl; ++l) {
+      GemmEpi b = pl.epi0();
+      b.kind = EPI_RESID; b.outf = m->sw_qkv + (size_t)l * 2560; b.ld_outf = nl * 2560;
+      pl.gemm("decoder_attn_qkv_w", nullptr, l, m->shift_attn_bf + (size_t)l * ns * 1024, ns, 1024, 1024, b);
+      b.outf = m->sw_gate + (size_t)l * 4096; b.ld_outf = nl * 4096;
+      pl.gemm("decoder_ffn_gate_w", nullptr, l, m->shift_ffn_bf + (size_t)l * ns * 1024, ns, 1024, 1024, b);
+      b.outf = m->sw_up + (size_t)l * 4096;
+      pl.gemm("decoder_ffn_up_w", nullptr, l, m->shift_ffn_bf + (size_t)l * ns * 1024, ns, 1024, 1024, b);
+    }
+  }
   int rc = VLA_OK;
   if (!pl.ok) rc = m->fail(VLA_ERR_CUDA, "pi05 precompute plan: %s", pl.err.c_str());
   else rc = run_ops(m, st);
