@@ -6,7 +6,7 @@ syntax tree and compiled into a stub class; nothing of them is copied into this 
 deterministic frames and statistics of oracle/preproc_oracle.py, so the test can rebuild them.
 
 Run in the build container (needs the reference checkout, PIL, einops):
-    python tests/golden/make_preproc_golden.py [/path/to/reference]
+    python tests/golden/make_preproc_golden.py /path/to/reference
 """
 import ast
 import os
@@ -47,7 +47,9 @@ def stats(seed, dim):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_preproc_golden.py /path/to/reference")
+    ref_root = sys.argv[1]
     Ref = reference_class(ref_root)
     out = {}
     for model in ("pi0", "pi05"):
