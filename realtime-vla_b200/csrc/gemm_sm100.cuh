@@ -90,6 +90,9 @@ struct GemmParams {
   int n_tok;         // valid tokens
   int k_blocks;      // Kp / 64
   int split;         // cluster size along K (1 = no cluster)
+  int tok_tile;      // tokens per CTA along grid.y, a multiple of 32 and <= BN (0 = BN): the host evens the tiles out
+                     // (788 tokens = 4 x 224 rather than 3 x 256 + 20) so that the last tile does not stream the
+                     // whole weight panel for a handful of tokens; the B box of tmB has this many rows
   int m256;          // launch of the PAIR variant: the two accumulators are two feature tiles of ONE weight
                      // (features feat0.. and feat0+128..) instead of the gate/up pair; each gets the plain epilogue
   int* status;       // device status word
@@ -287,13 +290,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   if (threadIdx.x == 0) GEMM_TRACE(0);
   const int split = SPLITK ? p.split : 1;
   const int rank = SPLITK ? (int)blockIdx.x : 0;  // == cluster rank: cluster dims are (split,1,1), gridDim.x == split
-  const int tok0 = blockIdx.y * BN;
+  const int tok_tile = p.tok_tile > 0 ? p.tok_tile : BN;
+  const int tok0 = blockIdx.y * tok_tile;
+  const uint32_t stage_tx = (uint32_t)(C::A_BYTES * (TWO ? 2 : 1) + tok_tile * 128);   // bytes one K block brings in
   const int feat0 = blockIdx.z * (m256 ? 256 : 128);
   const int kb_begin = (int)(((long long)rank * p.k_blocks) / split);
   const int kb_end = (int)(((long long)(rank + 1) * p.k_blocks) / split);
   const int n_iters = kb_end - kb_begin;
   int umma_n = p.n_tok - tok0;
-  umma_n = umma_n > BN ? BN : ((umma_n + 15) & ~15);
+  umma_n = umma_n > tok_tile ? tok_tile : ((umma_n + 15) & ~15);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -327,7 +332,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     for (int it = 0; it < n_pre; ++it) {
       const uint32_t st = smem_base + it * C::STAGE_BYTES;
       const int k0 = (kb_begin + it) * 64;
-      mbar_expect_tx(full_bar + 8 * it, C::STAGE_BYTES);
+      mbar_expect_tx(full_bar + 8 * it, stage_tx);
       tma_load_2d(st, &p.tmA, full_bar + 8 * it, k0, feat0, pol_w);
       if (TWO) tma_load_2d(st + C::A_BYTES, m256 ? &p.tmA : &p.tmA2, full_bar + 8 * it, k0, feat0 + (m256 ? 128 : 0), pol_w);
     }
@@ -347,7 +352,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         if (it >= n_pre) {
           const uint32_t ph = (uint32_t)(it / C::STAGES) & 1u;
           if (!mbar_wait(empty_bar + 8 * s, ph ^ 1u, abort_flag)) break;
-          mbar_expect_tx(full_bar + 8 * s, C::STAGE_BYTES);
+          mbar_expect_tx(full_bar + 8 * s, stage_tx);
           tma_load_2d(st, &p.tmA, full_bar + 8 * s, k0, feat0, pol_w);
           if (TWO) tma_load_2d(st + C::A_BYTES, m256 ? &p.tmA : &p.tmA2, full_bar + 8 * s, k0, feat0 + (m256 ? 128 : 0), pol_w);
         }

@@ -253,12 +253,20 @@ bool build_gemm(GemmOp* op, const bf16* w, const bf16* w2, int n_feat, int n_fea
   }
   op->p.m256 = m256;
   op->bn = bn;
-  const int tok_tiles = (tokens + bn - 1) / bn;
+  // Even out the token tiles: same number of tiles, each a multiple of 32 tokens (the epilogue's store blocks),
+  // so that no CTA streams the whole weight panel for a few leftover tokens.
+  int tok_tile = bn;
+  if (tokens > bn) {
+    const int n_tiles = (tokens + bn - 1) / bn;
+    tok_tile = std::min(bn, (((tokens + n_tiles - 1) / n_tiles) + 31) / 32 * 32);
+  }
+  op->p.tok_tile = tok_tile;
+  const int tok_tiles = (tokens + tok_tile - 1) / tok_tile;
   if (split > 1 && !can_split(bn, op->dual)) { *err = "this tile shape has no split-K variant"; return false; }
   if (split > 8 || split > kb || (split & (split - 1))) { *err = "split must be 1, 2, 4 or 8 and <= K/64"; return false; }
   if (!make_tmap(&op->p.tmA, w, Kp, n_feat_pad, Kp, 128, err)) return false;
   if (w2 && !make_tmap(&op->p.tmA2, w2, Kp, n_feat_pad, Kp, 128, err)) return false;
-  if (!make_tmap(&op->p.tmB, x, Kx, tokens, ldx, op->bn, err)) return false;
+  if (!make_tmap(&op->p.tmB, x, Kx, tokens, ldx, tok_tile, err)) return false;
   op->p.n_feat = n_feat;
   op->p.n_tok = tokens;
   op->p.k_blocks = kb;

@@ -133,7 +133,7 @@ GEMM_CASES = [
     (51, 1024, 2560, 1, 64), (51, 1024, 2560, 4, 64), (51, 2048, 1024, 8, 64), (51, 4096, 1024, 8, 0),
     (1, 1024, 1024, 1, 0), (50, 32, 1024, 1, 0), (10, 1024, 3072, 2, 64),
     (256, 1152, 3456, 4, 256), (256, 1152, 4304, 2, 0), (256, 640, 1152, 1, 0), (512, 4304, 1152, 8, 128),
-    (788, 2048, 2048, 1, 256), (788, 2048, 2048, 2, 128), (788, 2048, 2048, 0, 0), (256, 2048, 2560, 0, 0), (768, 1152, 3456, 0, 0), (300, 2048, 512, 8, 128), (100, 1152, 2048, 4, 128),
+    (788, 2048, 2048, 1, 256), (788, 2048, 2048, 2, 128), (564, 2048, 1024, 1, 256), (532, 1024, 1152, 2, 256), (330, 1152, 640, 1, 256), (788, 2048, 2048, 0, 0), (256, 2048, 2560, 0, 0), (768, 1152, 3456, 0, 0), (300, 2048, 512, 8, 128), (100, 1152, 2048, 4, 128),
 ]
 
 
