@@ -152,7 +152,8 @@ const char* vla_last_error(vla_handle h);
  * epi: 0 = bf16 out (+bias, act: 0 none, 1 gelu-tanh, 2 silu, 3 GeGLU with W2), 1 = fp32 residual
  * (outf = res + bias + gate*acc, in place when res == outf), 2 = QKV+RoPE (N must be 2560; q, kcache, vcache out, vt = optional transposed value cache [256, vt_ld]).
  * split = cluster size along K (0 = library heuristic), bn = token tile (0 = heuristic), pair = two 128-feature
- * tiles of W per CTA sharing the activation tile (0 = heuristic, 1 = force, -1 = never; ignored with W2). */
+ * tiles of W per CTA sharing the activation tile (0 = heuristic, 1 = force, -1 = never; ignored with W2),
+ * tok_tile = tokens per CTA (0 = heuristic: the token tiles are evened out; else a multiple of 32, <= bn). */
 typedef struct vla_gemm_desc {
   const void* x; int tokens; int K;
   const void* w; const void* w2; int N;
@@ -162,6 +163,7 @@ typedef struct vla_gemm_desc {
   void* q; void* kcache; void* vcache; void* vt; int vt_ld; int pos_off; int rows_per_obs; int kv_obs_stride; int kv_row_off;
   int split; int bn; int iters; float* ms_per_iter;
   int pair;
+  int tok_tile;
 } vla_gemm_desc;
 int vla_op_gemm(const vla_gemm_desc* d, void* stream);
 

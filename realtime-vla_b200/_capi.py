@@ -25,7 +25,7 @@ class GemmDesc(C.Structure):
                 ("q", C.c_void_p), ("kcache", C.c_void_p), ("vcache", C.c_void_p), ("vt", C.c_void_p), ("vt_ld", C.c_int),
                 ("pos_off", C.c_int), ("rows_per_obs", C.c_int), ("kv_obs_stride", C.c_int), ("kv_row_off", C.c_int),
                 ("split", C.c_int), ("bn", C.c_int), ("iters", C.c_int), ("ms_per_iter", C.POINTER(C.c_float)),
-                ("pair", C.c_int)]
+                ("pair", C.c_int), ("tok_tile", C.c_int)]
 
 
 class AttnDesc(C.Structure):

@@ -232,7 +232,7 @@ cudaError_t launch_gemm(const GemmOp& op, cudaStream_t st, bool pdl) {
 // w / w2: repacked weights [n_feat_pad, Kp]; x: activations [tokens, K] with pitch ldx.
 bool build_gemm(GemmOp* op, const bf16* w, const bf16* w2, int n_feat, int n_feat_pad, int Kp, const bf16* x, int tokens,
                 int Kx, int ldx, const GemmEpi& epi, int* status, int sm_count, int force_bn, int force_split,
-                std::string* err, int m256_mode = 0) {
+                std::string* err, int m256_mode = 0, int force_tok_tile = 0) {
   memset(op, 0, sizeof *op);
   op->dual = w2 != nullptr;
   if (Kp % 64 || n_feat_pad % 128) { *err = "repacked weight must be padded to 128 features x 64 K"; return false; }
@@ -259,6 +259,10 @@ bool build_gemm(GemmOp* op, const bf16* w, const bf16* w2, int n_feat, int n_fea
   if (tokens > bn) {
     const int n_tiles = (tokens + bn - 1) / bn;
     tok_tile = std::min(bn, (((tokens + n_tiles - 1) / n_tiles) + 31) / 32 * 32);
+  }
+  if (force_tok_tile > 0) {
+    if (force_tok_tile % 32 || force_tok_tile > bn) { *err = "token tile stride must be a multiple of 32 and <= bn"; return false; }
+    tok_tile = force_tok_tile;
   }
   op->p.tok_tile = tok_tile;
   const int tok_tiles = (tokens + tok_tile - 1) / tok_tile;
@@ -1538,7 +1542,7 @@ int vla_op_gemm(const vla_gemm_desc* d, void* stream) {
     e.vt = reinterpret_cast<bf16*>(d->vt); e.vt_ld = d->vt_ld;
   }
   if (!build_gemm(&op, wt, wt2, d->N, Np, Kp, reinterpret_cast<const bf16*>(d->x), d->tokens, d->K, d->K, e, status, sms,
-                  d->bn, d->split, &err, d->pair)) {
+                  d->bn, d->split, &err, d->pair, d->tok_tile)) {
     g_last_error = err;
     rc = VLA_ERR_SHAPE;
     goto done;

@@ -11,7 +11,7 @@ def _p(t):
     return C.c_void_p(t.data_ptr()) if t is not None else None
 
 
-def gemm(x, w, *, w2=None, bias=None, epi=0, act=0, res=None, gate=None, res_mod=0, split=0, bn=0, pair=0, iters=0,
+def gemm(x, w, *, w2=None, bias=None, epi=0, act=0, res=None, gate=None, res_mod=0, split=0, bn=0, pair=0, tok_tile=0, iters=0,
          qkv=None):
     """x bf16 [tokens,K], w bf16 [K,N] (checkpoint layout). Returns the epilogue's output tensor(s)."""
     lib = _capi.lib()
@@ -20,7 +20,7 @@ def gemm(x, w, *, w2=None, bias=None, epi=0, act=0, res=None, gate=None, res_mod
     d = _capi.GemmDesc()
     d.x, d.tokens, d.K, d.w, d.w2, d.N = _p(x), tokens, K, _p(w), _p(w2), N
     d.bias, d.epi, d.act = _p(bias), epi, act
-    d.split, d.bn, d.iters, d.pair = split, bn, iters, pair
+    d.split, d.bn, d.iters, d.pair, d.tok_tile = split, bn, iters, pair, tok_tile
     ms = C.c_float(0)
     d.ms_per_iter = C.pointer(ms)
     out = None
