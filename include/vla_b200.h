@@ -50,7 +50,8 @@ typedef struct vla_config {
   int n_vit_layers;   /* 0 -> 27 */
   int n_layers;       /* 0 -> 18 */
   int n_steps;        /* 0 -> 10 */
-  int flags;          /* bit 0: disable programmatic dependent launch; bit 1: run without a CUDA graph */
+  int flags;          /* bit 0: disable programmatic dependent launch; bit 1: run without a CUDA graph;
+                         bit 2: SigLIP attention on the legacy mma.sync kernel instead of tcgen05 */
 } vla_config;
 
 /* Replaces Pi0Inference.__init__ / Pi05Inference.__init__ up to buffer allocation (pi0_infer.py:1245-1317). */
@@ -189,6 +190,11 @@ typedef struct vla_attn_tc_desc {
   float scale; int ksplit; int iters; float* ms_per_iter;
 } vla_attn_tc_desc;
 int vla_op_attention_tc(const vla_attn_tc_desc* d, void* stream);
+
+/* SigLIP attention on the tcgen05 tensor cores (AttnMultiKey of the reference, pi0_infer.py:588-596): qkv bf16
+ * [views * 256, 3456] = [Q | K | V] with 16 heads of 72 each, o bf16 [views * 256, 1152]; per view and head
+ * softmax(Q K^T * scale) V over the view's 256 tokens, no mask. */
+int vla_op_vit_attention_tc(const void* qkv, void* o, int views, float scale, int iters, float* ms_per_iter, void* stream);
 
 /* Y = X[tokens,K] @ W + bias as bf16, for callers that must not allocate device memory: code running inside
  * a real-time control loop with a fixed memory budget, or on a thread that may not take the allocator's

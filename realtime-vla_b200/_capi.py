@@ -64,6 +64,7 @@ EXPORTS = {
     "vla_status_word": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
     "vla_stats": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_size_t)]),
     "vla_set_prompt_ids": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int]),
+    "vla_op_vit_attention_tc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_float, C.c_int, C.POINTER(C.c_float), C.c_void_p]),
     "vla_preprocess_image": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "vla_preprocess_state": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double),
                                        C.c_int, C.c_int, C.POINTER(C.c_double), C.c_void_p]),

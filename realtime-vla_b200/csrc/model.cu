@@ -19,6 +19,7 @@
 #include "../../include/vla_b200.h"
 #include "attention.cuh"
 #include "attention_tc.cuh"
+#include "attention_vit_tc.cuh"
 #include "elementwise.cuh"
 #include "gemm_sm100.cuh"
 #include "preprocess.cuh"
@@ -365,6 +366,17 @@ cudaError_t launch_attn_tc(const AttnTcOp& op, cudaStream_t st, bool pdl) {
     attr_set = true;
   }
   return launch_ex(attention_tc_kernel, op.grid, dim3(AttnTcCfg::THREADS), AttnTcCfg::SMEM_BYTES, st, op.p.ksplit, pdl, op.p);
+}
+
+// SigLIP attention of `views` camera views (16 heads x 72, 256 tokens each) on tcgen05
+cudaError_t launch_vit_attn_tc(const VitAttnTcParams& p, int views, cudaStream_t st, bool pdl) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(vit_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, VitAttnTcCfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  return launch_ex(vit_attention_tc_kernel, dim3(2, 16, views), dim3(VitAttnTcCfg::THREADS), VitAttnTcCfg::SMEM_BYTES, st, 1, pdl, p);
 }
 
 cudaError_t launch_norm(const float* x, int ld_x, bf16* y, int ld_y, int rows, int D, int mode, const float* w,
@@ -732,7 +744,14 @@ void plan_vision(Plan& pl) {
     a.q_go = a.k_go = a.v_go = 256LL * 3456; a.q_gi = a.k_gi = a.v_gi = 72; a.o_go = 256LL * 1152; a.o_gi = 72;
     a.g_inner = 16; a.n_q = 256; a.n_keys = 256; a.prefix_alloc = 256; a.valid_prefix = 256; a.restrict_rows = 0;
     a.scale_log2e = 1.4426950408889634f / sqrtf(72.f);
-    pl.attention(a, 72, m->B * m->nv * 16);
+    if (m->cfg.flags & 4) {
+      pl.attention(a, 72, m->B * m->nv * 16);     // legacy mma.sync kernel, kept for comparison
+    } else {
+      VitAttnTcParams vp;
+      vp.qkv = m->vision_qkv; vp.o = m->vision_attn; vp.scale_log2e = a.scale_log2e; vp.status = m->d_status;
+      const int views = m->B * m->nv;
+      pl.kernel([=](cudaStream_t st) { return launch_vit_attn_tc(vp, views, st, pdl); });
+    }
     e = pl.epi0();
     e.kind = EPI_RESID; e.bias = pl.vec("vision_attn_o_b", l); e.outf = m->vision_x; e.ld_outf = 1152; e.res_in = m->vision_x; e.ld_res = 1152;
     pl.gemm("vision_attn_o_w", nullptr, l, m->vision_attn, Nv, 1152, 1152, e);
@@ -1645,6 +1664,42 @@ done:
 // every GPU that loads the library from load time until exit and no call ever has to allocate it.
 #define VLA_NOALLOC_SCRATCH_FLOATS (1u << 20)   /* 4 MiB */
 static __device__ __align__(256) float vla_noalloc_scratch[VLA_NOALLOC_SCRATCH_FLOATS];
+
+int vla_op_vit_attention_tc(const void* qkv, void* o, int views, float scale, int iters, float* ms_per_iter, void* stream) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int rc = VLA_OK;
+  int* status = nullptr;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  VitAttnTcParams p;
+  if (!qkv || !o || views < 1) { g_last_error = "vla_op_vit_attention_tc: bad arguments"; return VLA_ERR_SHAPE; }
+  CKG(cudaMalloc(&status, sizeof(int)));
+  CKG(cudaMemsetAsync(status, 0, sizeof(int), st));
+  p.qkv = reinterpret_cast<const bf16*>(qkv); p.o = reinterpret_cast<bf16*>(o);
+  p.scale_log2e = scale * 1.4426950408889634f; p.status = status;
+  CKG(launch_vit_attn_tc(p, views, st, false));
+  if (iters > 0 && ms_per_iter) {
+    CKG(cudaEventCreate(&e0));
+    CKG(cudaEventCreate(&e1));
+    CKG(cudaEventRecord(e0, st));
+    for (int i = 0; i < iters; ++i) CKG(launch_vit_attn_tc(p, views, st, false));
+    CKG(cudaEventRecord(e1, st));
+    CKG(cudaEventSynchronize(e1));
+    float ms = 0.f;
+    CKG(cudaEventElapsedTime(&ms, e0, e1));
+    *ms_per_iter = ms / iters;
+  }
+  CKG(cudaStreamSynchronize(st));
+  {
+    int h = 0;
+    CKG(cudaMemcpy(&h, status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (h) { g_last_error = "vla_op_vit_attention_tc: device status word raised"; rc = VLA_ERR_DEVICE; }
+  }
+done:
+  if (e0) cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  if (status) cudaFree(status);
+  return rc;
+}
 
 int vla_op_gemm_noalloc(const vla_gemm_noalloc_desc* d, void* stream) {
   // Device address of the scratch array, looked up once per device.  In host code the array's name is only a

@@ -96,3 +96,14 @@ def norm(x, mode, w=None, b=None):
     y = torch.empty(rows, D, dtype=torch.bfloat16, device=x.device)
     _capi.check(lib.vla_op_norm(_p(x), _p(y), rows, D, mode, _p(w), _p(b), None))
     return y
+
+
+def vit_attention_tc(qkv, *, scale, iters=0):
+    """SigLIP attention on tcgen05: qkv bf16 [views*256, 3456] -> bf16 [views*256, 1152]."""
+    lib = _capi.lib()
+    views = qkv.shape[0] // 256
+    out = torch.full((views * 256, 1152), float("nan"), dtype=torch.bfloat16, device=qkv.device)
+    ms = C.c_float(0)
+    stream = torch.cuda.current_stream(qkv.device).cuda_stream
+    _capi.check(lib.vla_op_vit_attention_tc(_p(qkv), _p(out), views, float(scale), iters, C.byref(ms), C.c_void_p(stream)))
+    return (out, ms.value) if iters else out

@@ -233,3 +233,17 @@ def test_gemm_qkv_rope(tokens, K, pos_off, split):
     assert_close(vc[row_off:], y[:, 2304:], what="V")
     assert_close(vt[:, row_off:row_off + tokens].t(), y[:, 2304:], what="V transposed")
     assert kc[:row_off].abs().max().item() == 0 if row_off else True
+
+
+@pytest.mark.parametrize("views", [1, 3, 5])
+def test_vit_attention_tc(views):
+    """SigLIP attention on tcgen05 against plain softmax attention per view and head (pi0_infer.py:588-596)."""
+    import vla_ops as gpu_ops
+    d = dev()
+    qkv = rnd((views * 256, 3456), 1.0, 60 + views, d)
+    out = gpu_ops.vit_attention_tc(qkv, scale=72 ** -0.5)
+    x = qkv.float().reshape(views, 256, 3, 16, 72)
+    q, k, v = (x[:, :, i].permute(0, 2, 1, 3) for i in range(3))          # [views, 16, 256, 72]
+    p = torch.softmax(q @ k.transpose(-1, -2) * 72 ** -0.5, dim=-1)
+    ref = (p @ v).permute(0, 2, 1, 3).reshape(views * 256, 1152)
+    assert_close(out, ref, what="siglip attention")
