@@ -16,11 +16,18 @@
 #pragma once
 #include "attention_tc.cuh"
 
+#ifdef VLA_TRACE
+#define VIT_TRACE(slot) do { if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 128) p.trace[slot] = clock64(); } while (0)
+#else
+#define VIT_TRACE(slot) do {} while (0)
+#endif
+
 struct VitAttnTcParams {
   const bf16* qkv;   // [views * 256, 3456] = [Q | K | V], each 16 heads x 72
   bf16* o;           // [views * 256, 1152]
   float scale_log2e; // 72^-0.5 * log2(e)
   int* status;
+  long long* trace;  // development timeline (-DVLA_TRACE), normally null
 };
 
 struct VitAttnTcCfg {
@@ -64,6 +71,7 @@ __global__ void __launch_bounds__(VitAttnTcCfg::THREADS, 1) vit_attention_tc_ker
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row0 = blockIdx.x * 128, head = blockIdx.y, view = blockIdx.z;
+  VIT_TRACE(0);
 
   if (tid == 0) {
     mbar_init(s_done, 1);
@@ -79,44 +87,60 @@ __global__ void __launch_bounds__(VitAttnTcCfg::THREADS, 1) vit_attention_tc_ker
 
   pdl_trigger();
   pdl_wait();
+  VIT_TRACE(1);
 
   // ---------------- operands into the swizzled K-major layout ----------------
   // a row of a [rows x 128 B] K block holds eight 16-byte chunks; chunk c of row r sits at r*128 + ((c ^ (r & 7)) << 4)
   const bf16* base = p.qkv + (size_t)view * 256 * 3456 + head * 72;
   const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-  // Q: 128 rows x 10 chunks (9 of data + 1 of zeros completing the last 16 dims)
-  for (int i = tid; i < 128 * 10; i += C::THREADS) {
-    const int r = i / 10, c = i - r * 10;
-    const uint4 v = c < 9 ? *reinterpret_cast<const uint4*>(base + (size_t)(row0 + r) * 3456 + c * 8) : zero4;
-    const int kb = c >> 3, cc = c & 7;
-    *reinterpret_cast<uint4*>(pQ + kb * 16384 + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
+  // All global loads of a thread are issued before the first shared-memory store, so that they share one L2
+  // round trip: Q 5, K 10, V 9 vectors of 16 bytes per thread.
+  uint4 qv[5], kv[10], vv[9];
+#pragma unroll
+  for (int j = 0; j < 5; ++j) {      // Q: 128 rows x 10 chunks (9 of data + 1 of zeros completing the last 16 dims)
+    const int i = tid + j * C::THREADS, r = i / 10, c = i - r * 10;
+    qv[j] = c < 9 ? *reinterpret_cast<const uint4*>(base + (size_t)(row0 + r) * 3456 + c * 8) : zero4;
   }
-  // K: 256 keys x 10 chunks
-  for (int i = tid; i < 256 * 10; i += C::THREADS) {
-    const int r = i / 10, c = i - r * 10;
-    const uint4 v = c < 9 ? *reinterpret_cast<const uint4*>(base + 1152 + (size_t)r * 3456 + c * 8) : zero4;
-    const int kb = c >> 3, cc = c & 7;
-    *reinterpret_cast<uint4*>(pK + kb * 32768 + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
+#pragma unroll
+  for (int j = 0; j < 10; ++j) {     // K: 256 keys x 10 chunks
+    const int i = tid + j * C::THREADS, r = i / 10, c = i - r * 10;
+    kv[j] = c < 9 ? *reinterpret_cast<const uint4*>(base + 1152 + (size_t)r * 3456 + c * 8) : zero4;
+  }
+#pragma unroll
+  for (int j = 0; j < 9; ++j)        // V: key = tid, chunk j (consecutive threads take consecutive keys)
+    vv[j] = *reinterpret_cast<const uint4*>(base + 2304 + (size_t)tid * 3456 + j * 8);
+  VIT_TRACE(2);
+#pragma unroll
+  for (int j = 0; j < 5; ++j) {
+    const int i = tid + j * C::THREADS, r = i / 10, c = i - r * 10, kb = c >> 3, cc = c & 7;
+    *reinterpret_cast<uint4*>(pQ + kb * 16384 + r * 128 + ((cc ^ (r & 7)) << 4)) = qv[j];
+  }
+#pragma unroll
+  for (int j = 0; j < 10; ++j) {
+    const int i = tid + j * C::THREADS, r = i / 10, c = i - r * 10, kb = c >> 3, cc = c & 7;
+    *reinterpret_cast<uint4*>(pK + kb * 32768 + r * 128 + ((cc ^ (r & 7)) << 4)) = kv[j];
   }
   // V^T: element (d, key) of K block key/64 at d*128 + (((key%64)/8 ^ (d & 7)) << 4) + (key % 8) * 2; rows 72..79 zero
-  for (int i = tid; i < 8 * 4 * 8; i += C::THREADS) {   // 8 zero rows x 4 K blocks x 8 chunks
+  {
+    const int i = tid;                 // 8 zero rows x 4 K blocks x 8 chunks = 256 vectors
     const int d = 72 + (i >> 5), kb = (i >> 3) & 3, cc = i & 7;
     *reinterpret_cast<uint4*>(pV + kb * 10240 + d * 128 + (cc << 4)) = zero4;
-  }
-  for (int i = tid; i < 256 * 9; i += C::THREADS) {
-    const int key = i & 255, c = i >> 8;       // consecutive threads take consecutive keys of one 8-dim chunk
-    const uint4 v = *reinterpret_cast<const uint4*>(base + 2304 + (size_t)key * 3456 + c * 8);
-    const bf16* e = reinterpret_cast<const bf16*>(&v);
+    const int key = tid, kc = (key & 63) >> 3;
     uint8_t* blk = pV + (key >> 6) * 10240 + (key & 7) * 2;
-    const int kc = (key & 63) >> 3;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int d = c * 8 + j;
-      *reinterpret_cast<bf16*>(blk + d * 128 + ((kc ^ (d & 7)) << 4)) = e[j];
+    for (int c = 0; c < 9; ++c) {
+      const bf16* e = reinterpret_cast<const bf16*>(&vv[c]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int d2 = c * 8 + j;
+        *reinterpret_cast<bf16*>(blk + d2 * 128 + ((kc ^ (d2 & 7)) << 4)) = e[j];
+      }
     }
   }
+  VIT_TRACE(3);
   fence_proxy_async_smem();   // generic-proxy stores -> visible to the tensor core's async-proxy reads
   __syncthreads();
+  VIT_TRACE(4);
 
   // ---------------- S = Q K^T ----------------
   if (warp == 0 && lane == 0) {
@@ -137,18 +161,20 @@ __global__ void __launch_bounds__(VitAttnTcCfg::THREADS, 1) vit_attention_tc_ker
   const uint32_t lane_off = (uint32_t)(q * 32) << 16;
   bool ok = __all_sync(0xffffffffu, mbar_wait(s_done, 0, abort_flag));   // TMEM loads are warp-collective
   tc_fence_after();
+  VIT_TRACE(5);
+  // the 128 logits of this thread stay in registers between the two passes
+  uint32_t sv[128];
   float m_loc = -1e30f;
   if (ok) {
-#pragma unroll 1
-    for (int c0 = 0; c0 < 128; c0 += 32) {
-      uint32_t v[32];
-      tmem_ld32(tmem_S + lane_off + half * 128 + c0, v);
-      tmem_ld_wait();
-      float mx[4] = {-3.0e38f, -3.0e38f, -3.0e38f, -3.0e38f};
 #pragma unroll
-      for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(v[j]));
-      m_loc = fmaxf(m_loc, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2e);
-    }
+    for (int c0 = 0; c0 < 128; c0 += 32) tmem_ld32(tmem_S + lane_off + half * 128 + c0, sv + c0);
+    tmem_ld_wait();
+    float mx[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) mx[j] = -3.0e38f;
+#pragma unroll
+    for (int j = 0; j < 128; ++j) mx[j & 7] = fmaxf(mx[j & 7], __uint_as_float(sv[j]));
+    m_loc = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7]))) * p.scale_log2e;
   }
   xchg[half * 128 + r] = m_loc;
   named_barrier_sync(1 + q, 64);      // the two warps of this lane quarter
@@ -156,17 +182,14 @@ __global__ void __launch_bounds__(VitAttnTcCfg::THREADS, 1) vit_attention_tc_ker
   named_barrier_sync(1 + q, 64);      // both have read the maxima before the sums reuse the slots
   float l_loc = 0.f;
   if (ok) {
-#pragma unroll 1
+#pragma unroll
     for (int c0 = 0; c0 < 128; c0 += 32) {
-      uint32_t v[32];
-      tmem_ld32(tmem_S + lane_off + half * 128 + c0, v);
-      tmem_ld_wait();
       uint32_t pk[16];
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int j = 0; j < 32; j += 2) {
-        const float e0 = ex2_approx(fmaf(__uint_as_float(v[j]), p.scale_log2e, -m_row));
-        const float e1 = ex2_approx(fmaf(__uint_as_float(v[j + 1]), p.scale_log2e, -m_row));
+        const float e0 = ex2_approx(fmaf(__uint_as_float(sv[c0 + j]), p.scale_log2e, -m_row));
+        const float e1 = ex2_approx(fmaf(__uint_as_float(sv[c0 + j + 1]), p.scale_log2e, -m_row));
         const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
         ls[(j >> 1) & 3] += __bfloat162float(h.x) + __bfloat162float(h.y);   // sum of what the P V product sees
         pk[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
@@ -180,6 +203,7 @@ __global__ void __launch_bounds__(VitAttnTcCfg::THREADS, 1) vit_attention_tc_ker
         *reinterpret_cast<uint4*>(tile + (((cbase + g) ^ (r & 7)) << 4)) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
     }
   }
+  VIT_TRACE(6);
   xchg[half * 128 + r] = l_loc;
   fence_proxy_async_smem();
   tc_fence_before();
@@ -201,6 +225,7 @@ __global__ void __launch_bounds__(VitAttnTcCfg::THREADS, 1) vit_attention_tc_ker
   __syncwarp();
   ok = ok && __all_sync(0xffffffffu, mbar_wait(o_done, 0, abort_flag));
   tc_fence_after();
+  VIT_TRACE(7);
   if (ok) {
     // half 0 stores dims 0..31 and 64..71, half 1 dims 32..63 (80 accumulator columns, the last 8 are padding)
     const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
@@ -229,6 +254,7 @@ __global__ void __launch_bounds__(VitAttnTcCfg::THREADS, 1) vit_attention_tc_ker
   }
 
   // ---------------- teardown ----------------
+  VIT_TRACE(8);
   tc_fence_before();
   __syncthreads();
   if (*abort_flag) {

@@ -751,7 +751,7 @@ void plan_vision(Plan& pl) {
       pl.attention(a, 72, m->B * m->nv * 16);
     } else {
       VitAttnTcParams vp;
-      vp.qkv = m->vision_qkv; vp.o = m->vision_attn; vp.scale_log2e = a.scale_log2e; vp.status = m->d_status;
+      vp.qkv = m->vision_qkv; vp.o = m->vision_attn; vp.scale_log2e = a.scale_log2e; vp.status = m->d_status; vp.trace = nullptr;
       const int views = m->B * m->nv;
       pl.kernel([=](cudaStream_t st) { return launch_vit_attn_tc(vp, views, st, pdl); });
     }
@@ -1678,8 +1678,26 @@ int vla_op_vit_attention_tc(const void* qkv, void* o, int views, float scale, in
   CKG(cudaMalloc(&status, sizeof(int)));
   CKG(cudaMemsetAsync(status, 0, sizeof(int), st));
   p.qkv = reinterpret_cast<const bf16*>(qkv); p.o = reinterpret_cast<bf16*>(o);
-  p.scale_log2e = scale * 1.4426950408889634f; p.status = status;
+  p.scale_log2e = scale * 1.4426950408889634f; p.status = status; p.trace = nullptr;
   CKG(launch_vit_attn_tc(p, views, st, false));
+#ifdef VLA_TRACE
+  {
+    long long* tr = nullptr;
+    CKG(cudaMalloc(&tr, 16 * sizeof(long long)));
+    CKG(cudaMemset(tr, 0, 16 * sizeof(long long)));
+    for (int rep = 0; rep < 3; ++rep) CKG(launch_vit_attn_tc(p, views, st, false));
+    p.trace = tr;
+    CKG(launch_vit_attn_tc(p, views, st, false));
+    p.trace = nullptr;
+    CKG(cudaStreamSynchronize(st));
+    long long h[16];
+    CKG(cudaMemcpy(h, tr, sizeof h, cudaMemcpyDeviceToHost));
+    cudaFree(tr);
+    fprintf(stderr, "vit attention timeline (cycles after entry):");
+    for (int i = 1; i <= 8; ++i) fprintf(stderr, " %lld", h[i] - h[0]);
+    fprintf(stderr, "\n");
+  }
+#endif
   if (iters > 0 && ms_per_iter) {
     CKG(cudaEventCreate(&e0));
     CKG(cudaEventCreate(&e1));
