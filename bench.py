@@ -33,6 +33,8 @@ WORKLOADS = {
     "cfg1": dict(model="pi0", num_views=1, prompt_len=0, chunk=50, seed=0),
     "cfg2": dict(model="pi0", num_views=3, prompt_len=20, chunk=50, seed=0),
     "cfg3": dict(model="pi05", num_views=2, prompt_len=52, chunk=50, seed=1),
+    # Pi05 at the shape the reference's benchmark.py was timed on this GPU type (3 views, 20 prompt tokens)
+    "pi05_3v": dict(model="pi05", num_views=3, prompt_len=20, chunk=50, seed=1),
     # action expert alone over a prefilled K/V cache (the weight-streaming stage): stage mask 4 of the forward
     "cfg4": dict(model="pi0", num_views=3, prompt_len=20, chunk=50, seed=0, stages=4),
     # throughput mode: 32 independent observations per forward on each GPU
@@ -42,7 +44,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from the ncu
 # capture summarised under profiles/), keyed by workload; None until a capture exists.
-NCU_TRAFFIC_BYTES = {"cfg2": 144486144, "cfg1": None, "cfg3": None, "cfg4": None, "cfg5": None}   # profiles/gemm_sm100_geglu_prefix_p788.md
+NCU_TRAFFIC_BYTES = {"cfg2": 144486144, "cfg1": None, "cfg3": None, "cfg4": None, "cfg5": None, "pi05_3v": None}   # profiles/gemm_sm100_geglu_prefix_p788.md
 
 
 def peaks():
