@@ -51,7 +51,8 @@ typedef struct vla_config {
   int n_layers;       /* 0 -> 18 */
   int n_steps;        /* 0 -> 10 */
   int flags;          /* bit 0: disable programmatic dependent launch; bit 1: run without a CUDA graph;
-                         bit 2: SigLIP attention on the legacy mma.sync kernel instead of tcgen05 */
+                         bit 2: SigLIP attention on the legacy mma.sync kernel instead of tcgen05;
+                         bit 3: prefix / suffix attention of batched forwards on the legacy mma.sync kernel */
 } vla_config;
 
 /* Replaces Pi0Inference.__init__ / Pi05Inference.__init__ up to buffer allocation (pi0_infer.py:1245-1317). */

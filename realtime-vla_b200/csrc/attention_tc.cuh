@@ -32,8 +32,11 @@ struct AttnTcParams {
   int restrict_rows;
   float scale_log2e;
   int ksplit;
-  float* scratch;     // [row block][rank][260 columns][128 rows] fp32 when ksplit > 1
+  float* scratch;     // [group][row block][rank][260 columns][128 rows] fp32 when ksplit > 1
   int* status;
+  // groups = independent observations along grid.z: group g uses query/output rows g*q_group_rows.., key rows
+  // g*k_group_rows.. and rows g*256.. of the transposed value tensor; masks and lengths are the same for all
+  int q_group_rows, k_group_rows;
 };
 
 struct AttnTcCfg {
@@ -102,6 +105,7 @@ __global__ void __launch_bounds__(AttnTcCfg::THREADS, 1) attention_tc_kernel(con
   KTRACE(20);
   const int rank = blockIdx.x, ksplit = p.ksplit;
   const int row0 = blockIdx.y * 128;
+  const int q_base = blockIdx.z * p.q_group_rows, k_base = blockIdx.z * p.k_group_rows, vt_base = blockIdx.z * 256;
   const int n_chunks_total = (p.n_keys + 127) / 128;
   const int ch_begin = (int)(((long long)rank * n_chunks_total) / ksplit);
   const int ch_end = (int)(((long long)(rank + 1) * n_chunks_total) / ksplit);
@@ -135,17 +139,17 @@ __global__ void __launch_bounds__(AttnTcCfg::THREADS, 1) attention_tc_kernel(con
     if (lane == 0 && n_chunks > 0) {
       const uint64_t pol = policy_evict_last();
       mbar_expect_tx(q_full, C::Q_BYTES);
-      for (int kb = 0; kb < 4; ++kb) tma_load_2d(sQ + kb * 16384, &p.tmQ, q_full, kb * 64, row0, pol);
+      for (int kb = 0; kb < 4; ++kb) tma_load_2d(sQ + kb * 16384, &p.tmQ, q_full, kb * 64, q_base + row0, pol);
       for (int c = 0; c < n_chunks; ++c) {
         const int key0 = (ch_begin + c) * 128;
         // K buffer is free once the S MMAs of the previous chunk have completed
         if (c > 0 && !mbar_wait(s_full, (uint32_t)(c - 1) & 1u, abort_flag)) break;
         mbar_expect_tx(k_full, C::K_BYTES);
-        for (int kb = 0; kb < 4; ++kb) tma_load_2d(sK + kb * 16384, &p.tmK, k_full, kb * 64, key0, pol);
+        for (int kb = 0; kb < 4; ++kb) tma_load_2d(sK + kb * 16384, &p.tmK, k_full, kb * 64, k_base + key0, pol);
         // V buffer is free once the PV MMAs of the previous chunk have completed
         if (c > 0 && !mbar_wait(o_done, (uint32_t)(c - 1) & 1u, abort_flag)) break;
         mbar_expect_tx(v_full, C::V_BYTES);
-        for (int kb = 0; kb < 2; ++kb) tma_load_2d(sV + kb * 32768, &p.tmVt, v_full, key0 + kb * 64, 0, pol);
+        for (int kb = 0; kb < 2; ++kb) tma_load_2d(sV + kb * 32768, &p.tmVt, v_full, key0 + kb * 64, vt_base, pol);
         KTRACE_B(23, 0, p.ksplit - 1);
       }
     }
@@ -320,7 +324,7 @@ __global__ void __launch_bounds__(AttnTcCfg::THREADS, 1) attention_tc_kernel(con
       if (ok && n_chunks > 0) {
         const bool row_ok = i < p.n_q;
         const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-        bf16* orow = p.o + (size_t)(row_ok ? i : 0) * p.ldo + half * 128;
+        bf16* orow = p.o + (size_t)(q_base + (row_ok ? i : 0)) * p.ldo + half * 128;
 #pragma unroll 1
         for (int c0 = 0; c0 < 128; c0 += 32) {
           uint32_t v[32];
@@ -344,7 +348,7 @@ __global__ void __launch_bounds__(AttnTcCfg::THREADS, 1) attention_tc_kernel(con
   } else {
     // ---- merge the key splits through the L2-resident scratch, fixed rank order ----
     // layout per split: [260 columns][128 rows]: 256 outputs, max, row sum of half 0, row sum of half 1
-    float* cl = p.scratch + (size_t)blockIdx.y * ksplit * C::SCOLS * 128;
+    float* cl = p.scratch + (size_t)(blockIdx.z * gridDim.y + blockIdx.y) * ksplit * C::SCOLS * 128;
     if (is_sm) {
       float* mine = cl + (size_t)rank * C::SCOLS * 128;
       const bool live = ok && n_chunks > 0;
@@ -415,7 +419,7 @@ __global__ void __launch_bounds__(AttnTcCfg::THREADS, 1) attention_tc_kernel(con
         wv.y = pack_bf16(o[2] * inv, o[3] * inv);
         wv.z = pack_bf16(o[4] * inv, o[5] * inv);
         wv.w = pack_bf16(o[6] * inv, o[7] * inv);
-        *reinterpret_cast<uint4*>(p.o + (size_t)(row0 + rr) * p.ldo + d0) = wv;
+        *reinterpret_cast<uint4*>(p.o + (size_t)(q_base + row0 + rr) * p.ldo + d0) = wv;
       }
     }
   }

@@ -333,29 +333,33 @@ struct AttnTcOp {
   AttnTcParams p;
   dim3 grid;
 };
-int pick_ksplit_tc(int n_q, int n_keys, int sm_count) {
-  const int row_blocks = (n_q + 127) / 128, chunks = (n_keys + 127) / 128;
+int pick_ksplit_tc(int n_q, int n_keys, int sm_count, int groups = 1) {
+  const int row_blocks = ((n_q + 127) / 128) * groups, chunks = (n_keys + 127) / 128;
   int ks = 1;
   while (ks < 8 && ks < chunks && row_blocks * ks * 2 <= sm_count) ks *= 2;
   return ks;
 }
-size_t attn_tc_scratch_floats(int n_q, int ksplit) {
-  return ksplit > 1 ? (size_t)((n_q + 127) / 128) * ksplit * 128 * AttnTcCfg::SCOLS : 0;
+size_t attn_tc_scratch_floats(int n_q, int ksplit, int groups = 1) {
+  return ksplit > 1 ? (size_t)groups * ((n_q + 127) / 128) * ksplit * 128 * AttnTcCfg::SCOLS : 0;
 }
 // q [n_q,256]; k [k_rows,256] (n_keys <= k_rows used); vt [256, vt_ld] transposed values
 bool build_attn_tc(AttnTcOp* op, const bf16* q, const bf16* k, int k_rows, const bf16* vt, int vt_ld, bf16* o, int ldo, int n_q,
                    int n_keys, int prefix_alloc, int valid_prefix, const int* valid_ptr, int restrict_rows, float scale,
-                   int ksplit, float* scratch, int* status, std::string* err) {
+                   int ksplit, float* scratch, int* status, std::string* err, int groups = 1, int q_group_rows = 0) {
   memset(op, 0, sizeof *op);
   if (vt_ld % 8) { *err = "transposed value cache pitch must be a multiple of 8"; return false; }
-  if (!make_tmap(&op->p.tmQ, q, 256, n_q, 256, 128, err)) return false;
-  if (!make_tmap(&op->p.tmK, k, 256, k_rows, 256, 128, err)) return false;
-  if (!make_tmap(&op->p.tmVt, vt, vt_ld, 256, vt_ld, 256, err)) return false;
+  if (groups < 1) { *err = "attention needs at least one group"; return false; }
+  if (groups == 1) q_group_rows = n_q;
+  // groups: q [groups * q_group_rows, 256], k [groups * k_rows, 256], vt [groups * 256, vt_ld]
+  if (!make_tmap(&op->p.tmQ, q, 256, (groups - 1) * q_group_rows + n_q, 256, 128, err)) return false;
+  if (!make_tmap(&op->p.tmK, k, 256, groups * k_rows, 256, 128, err)) return false;
+  if (!make_tmap(&op->p.tmVt, vt, vt_ld, groups * 256, vt_ld, 256, err)) return false;
+  op->p.q_group_rows = q_group_rows; op->p.k_group_rows = k_rows;
   op->p.o = o; op->p.ldo = ldo; op->p.n_q = n_q; op->p.n_keys = n_keys;
   op->p.prefix_alloc = prefix_alloc; op->p.valid_prefix = valid_prefix; op->p.valid_prefix_ptr = valid_ptr;
   op->p.restrict_rows = restrict_rows; op->p.scale_log2e = scale * 1.4426950408889634f;
   op->p.ksplit = ksplit; op->p.scratch = scratch; op->p.status = status;
-  op->grid = dim3(ksplit, (n_q + 127) / 128, 1);
+  op->grid = dim3(ksplit, (n_q + 127) / 128, groups);
   return true;
 }
 cudaError_t launch_attn_tc(const AttnTcOp& op, cudaStream_t st, bool pdl) {
@@ -686,14 +690,15 @@ struct Plan {
     const bool pdl = m->use_pdl;
     kernel([=](cudaStream_t st) { return launch_norm(x, D, y, D, rows, D, mode, w, b, in_rpo, in_stride, in_off, st, pdl); });
   }
+  // one group per observation: q / o rows g*n_q.., cache rows g*T.., transposed values rows g*256..
   void attention_tc(const bf16* q, const bf16* k, const bf16* vt, bf16* o, int n_q, int n_keys, const int* valid_ptr,
-                    int restrict_rows) {
+                    int restrict_rows, int groups = 1) {
     if (!ok) return;
     AttnTcOp op;
-    const int ks = pick_ksplit_tc(n_q, n_keys, m->sm_count);
-    if (attn_tc_scratch_floats(n_q, ks) > m->attn_scratch_cap) { ok = false; err = "attention scratch too small"; return; }
+    const int ks = pick_ksplit_tc(n_q, n_keys, m->sm_count, groups);
+    if (attn_tc_scratch_floats(n_q, ks, groups) > m->attn_scratch_cap) { ok = false; err = "attention scratch too small"; return; }
     if (!build_attn_tc(&op, q, k, m->T, vt, m->T_pad, o, 256, n_q, n_keys, m->P, m->P, valid_ptr, restrict_rows, 1.0f / 16.0f,
-                       ks, m->attn_scratch, m->d_status, &err)) {
+                       ks, m->attn_scratch, m->d_status, &err, groups, n_q)) {
       ok = false;
       return;
     }
@@ -812,7 +817,7 @@ void plan_prefix(Plan& pl) {
     a.g_inner = 1; a.n_q = m->P * 8; a.n_keys = m->P; a.prefix_alloc = m->P; a.valid_prefix = m->P;
     a.valid_prefix_ptr = m->pi05 ? m->d_valid_len : nullptr;
     a.scale_log2e = 1.4426950408889634f / 16.f;
-    if (m->B == 1) pl.attention_tc(m->encoder_q, kc, vt, m->encoder_attn, m->P * 8, m->P, m->pi05 ? m->d_valid_len : nullptr, 0);
+    if (m->B == 1 || !(m->cfg.flags & 8)) pl.attention_tc(m->encoder_q, kc, vt, m->encoder_attn, m->P * 8, m->P, m->pi05 ? m->d_valid_len : nullptr, 0, m->B);
     else pl.attention(a, 256, m->B);
     e = pl.epi0();
     e.kind = EPI_RESID; e.outf = m->encoder_x; e.ld_outf = 2048; e.res_in = m->encoder_x; e.ld_res = 2048;
@@ -893,7 +898,7 @@ void plan_decoder(Plan& pl) {
       a.valid_prefix_ptr = pi05 ? m->d_valid_len : nullptr;
       a.restrict_rows = pi05 ? 0 : 8;
       a.scale_log2e = 1.4426950408889634f / 16.f;
-      if (B == 1) pl.attention_tc(m->decoder_q, kc, vt, m->decoder_attn, S * 8, m->T, pi05 ? m->d_valid_len : nullptr, pi05 ? 0 : 8);
+      if (B == 1 || !(m->cfg.flags & 8)) pl.attention_tc(m->decoder_q, kc, vt, m->decoder_attn, S * 8, m->T, pi05 ? m->d_valid_len : nullptr, pi05 ? 0 : 8, B);
       else pl.attention(a, 256, B);
       e = pl.epi0();
       e.kind = EPI_RESID; e.outf = m->decoder_x; e.ld_outf = 1024; e.res_in = m->decoder_x; e.ld_res = 1024;
