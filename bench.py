@@ -208,6 +208,18 @@ def expert_attention_timing(wl, device):
             "achieved": round(flops / (ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s", "ms_per_launch": round(ms, 5)}
 
 
+def siglip_attention_timing(wl, device):
+    """SigLIP attention of one ViT layer: num_views x 16 heads x (256 x 256) at head dim 72 on the tcgen05 kernel."""
+    import vla_ops
+    nv = wl["num_views"]
+    g = torch.Generator(device=device).manual_seed(9)
+    qkv = torch.randn(nv * 256, 3456, generator=g, device=device).to(torch.bfloat16)
+    _, ms = vla_ops.vit_attention_tc(qkv, scale=72 ** -0.5, iters=50)
+    flops = 4.0 * nv * 16 * 256 * 256 * 72
+    return {"kernel": "vit_attention_tc_kernel views=%d heads=16 tokens=256 head_dim=72" % nv, "bound": "latency",
+            "achieved": round(flops / (ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s", "ms_per_launch": round(ms, 5)}
+
+
 def preprocess_timing(wl, device):
     """Camera frames -> model input on the device (vla_preprocess_image: Pillow-exact bilinear resize, pad,
     normalise, bf16) for 640 x 480 frames, one per view: device time with the frames resident, end-to-end time from
@@ -428,10 +440,11 @@ def main():
                     help="replicas: every rank runs whole forwards (default); latency: one observation, one SigLIP tower "
                          "per rank + gather (needs at least num_views ranks)")
     ap.add_argument("--flags", type=int, default=0, help="vla_config.flags: 1 = no programmatic dependent launch, 2 = no CUDA graph")
-    ap.add_argument("--microbench", nargs="?", const="geglu", default=None, choices=["geglu", "expert_down", "expert_attention", "preprocess"],
+    ap.add_argument("--microbench", nargs="?", const="geglu", default=None, choices=["geglu", "expert_down", "expert_attention", "siglip_attention", "preprocess"],
                     help="time one kernel alone and print its roofline object: geglu = the dominant kernel of the workload "
                          "(prefix GeGLU GEMM); expert_down = action-expert down projection (51 x 4096 -> 1024, HBM-bound weight "
-                         "stream); expert_attention = suffix attention of the action expert on the tcgen05 kernel; preprocess = camera "
+                         "stream); expert_attention = suffix attention of the action expert on the tcgen05 kernel; siglip_attention = "
+                         "attention of one SigLIP layer on the tcgen05 kernel; preprocess = camera "
                          "frames -> model input (resize, pad, normalise) on the device against the host code")
     ap.add_argument("--profile-forward", action="store_true",
                     help="run two forwards and bracket the second with cudaProfilerStart/Stop (for ncu "
@@ -452,7 +465,7 @@ def main():
     device = torch.device("cuda", local)
     if args.microbench:
         fn = {"geglu": dominant_kernel_roofline, "expert_down": expert_down_roofline, "expert_attention": expert_attention_timing,
-              "preprocess": preprocess_timing}
+              "siglip_attention": siglip_attention_timing, "preprocess": preprocess_timing}
         print(json.dumps(fn[args.microbench](wl, device)), flush=True)
         return
     dist = None
