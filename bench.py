@@ -436,6 +436,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=0, help="override the observations per forward of a Pi0 workload (throughput mode)")
     ap.add_argument("--mode", default="replicas", choices=["replicas", "latency"],
                     help="replicas: every rank runs whole forwards (default); latency: one observation, one SigLIP tower "
                          "per rank + gather (needs at least num_views ranks)")
@@ -450,7 +451,9 @@ def main():
                     help="run two forwards and bracket the second with cudaProfilerStart/Stop (for ncu "
                          "--profile-from-start off); prints no benchmark line")
     args = ap.parse_args()
-    wl = WORKLOADS[args.workload]
+    wl = dict(WORKLOADS[args.workload])
+    if args.batch > 0:
+        wl["batch"] = args.batch
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
