@@ -76,6 +76,36 @@ def test_pi0_small_intermediates(small_pi0):
     check_actions(out, want)
 
 
+@pytest.mark.parametrize("model,nv,chunk,n_prompt", [("pi0", 2, 10, 0), ("pi0", 1, 100, 3), ("pi0", 3, 63, 17), ("pi0", 1, 1, 2),
+                                                    ("pi05", 2, 16, 7), ("pi05", 1, 120, 1), ("pi05", 3, 64, 30)])
+def test_other_shapes(model, nv, chunk, n_prompt):
+    """Chunk sizes other than 50 (suffix token counts on both sides of the 64- and 128-token tiles), every number
+    of views, short and empty prompts: reduced-depth models against the oracle."""
+    d = dev()
+    ck = synth.make_checkpoint(model, seed=3, prompt_ids=synth.prompt_ids(n_prompt, 4), n_vit_layers=1, n_layers=2)
+    images, state, noise = synth.make_inputs(nv, chunk, 2)
+    w = {k: v.to(d).float() for k, v in ck.items()}
+    vx = O.vision_encoder(w, images.to(d).float(), n_layers=1)
+    enc = torch.cat([O.project_vision(w, vx), w["language_embeds"].reshape(-1, 2048)], 0)
+    P = nv * 256 + n_prompt
+    if model == "pi0":
+        from pi0_infer import Pi0Inference
+        infer = Pi0Inference(ck, nv, chunk, n_vit_layers=1, n_layers=2, n_steps=3)
+        out = infer.forward(images, state, noise).clone()
+        K, V = O.prefix_encoder(w, enc, n_layers=2)
+        want = O.pi0_decoder(w, K, V, state.to(d).float(), noise.to(d).float(), n_layers=2, n_steps=3)
+    else:
+        from pi05_infer import Pi05Inference
+        infer = Pi05Inference(ck, nv, chunk, discrete_state_input=False, n_vit_layers=1, n_layers=2, n_steps=3)
+        out = infer.forward(images, noise).clone()
+        K, V = O.prefix_encoder(w, enc, valid_len=P, n_layers=2)
+        want = O.pi05_decoder(w, K, V, noise.to(d).float(), P, n_layers=2, n_steps=3)
+    torch.cuda.synchronize()
+    assert infer._engine.status_word() == 0
+    assert out.shape == (chunk, 32)
+    check_actions(out, want)
+
+
 def test_pi0_api_semantics(small_pi0):
     from pi0_infer import Pi0Inference
     dev()
