@@ -6,8 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(HERE, "libvla_b200.so")
 SOURCES = ["csrc/model.cu"]
-HEADERS = ["csrc/common.cuh", "csrc/gemm_sm100.cuh", "csrc/attention.cuh", "csrc/elementwise.cuh",
-           "../include/vla_b200.h"]
+HEADERS = sorted("csrc/" + f for f in os.listdir(os.path.join(HERE, "csrc")) if f.endswith(".cuh")) + ["../include/vla_b200.h"]
 
 
 def needs_build():
