@@ -106,6 +106,46 @@ def test_other_shapes(model, nv, chunk, n_prompt):
     check_actions(out, want)
 
 
+@pytest.mark.parametrize("model", ["pi0", "pi05"])
+def test_outlier_channels(model):
+    """Residual streams of trained transformers carry a few channels that are orders of magnitude larger than the
+    rest.  The folded norms keep an un-normalised bf16 copy of the stream, so check that such channels (output
+    features of the residual projections scaled x40, everywhere in the ViT, the prefix and the expert) do not
+    cost accuracy: same tolerance as for the plain synthetic weights, relative to the size of the actions."""
+    d = dev()
+    ck = synth.make_checkpoint(model, seed=5, prompt_ids=synth.prompt_ids(6, 5), n_vit_layers=2, n_layers=3)
+    g = torch.Generator().manual_seed(99)
+    for k in ("vision_attn_o_w", "vision_ffn_down_w", "encoder_attn_o_w", "encoder_ffn_down_w", "decoder_attn_o_w", "decoder_ffn_down_w"):
+        w = ck[k].float()
+        cols = torch.randperm(w.shape[-1], generator=g)[:6]
+        w[..., cols] *= 40.0
+        ck[k] = w.to(torch.bfloat16)
+    images, state, noise = synth.make_inputs(2, 50, 6)
+    if model == "pi0":
+        from pi0_infer import Pi0Inference
+        infer = Pi0Inference(ck, 2, 50, n_vit_layers=2, n_layers=3, n_steps=3)
+        out = infer.forward(images, state, noise).clone()
+        w = {k: v.to(d).float() for k, v in ck.items()}
+        vx = O.vision_encoder(w, images.to(d).float(), n_layers=2)
+        enc = torch.cat([O.project_vision(w, vx), w["language_embeds"]], 0)
+        K, V = O.prefix_encoder(w, enc, n_layers=3)
+        want = O.pi0_decoder(w, K, V, state.to(d).float(), noise.to(d).float(), n_layers=3, n_steps=3)
+    else:
+        from pi05_infer import Pi05Inference
+        infer = Pi05Inference(ck, 2, 50, discrete_state_input=False, n_vit_layers=2, n_layers=3, n_steps=3)
+        out = infer.forward(images, noise).clone()
+        w = {k: v.to(d).float() for k, v in ck.items()}
+        vx = O.vision_encoder(w, images.to(d).float(), n_layers=2)
+        enc = torch.cat([O.project_vision(w, vx), w["language_embeds"]], 0)
+        K, V = O.prefix_encoder(w, enc, valid_len=512 + 6, n_layers=3)
+        want = O.pi05_decoder(w, K, V, noise.to(d).float(), 512 + 6, n_layers=3, n_steps=3)
+    torch.cuda.synchronize()
+    assert infer._engine.status_word() == 0
+    stream_max = infer._engine.buffer("decoder_x", (50 + (model == "pi0"), 1024), torch.float32).abs().max().item()
+    print("largest residual-stream value in the expert: %.1f" % stream_max)
+    check_actions(out, want)
+
+
 def test_pi0_api_semantics(small_pi0):
     from pi0_infer import Pi0Inference
     dev()
