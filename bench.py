@@ -296,8 +296,20 @@ def decoder_stream(wl, decoder_ms):
             "unit": "GB/s", "frac": round(gbs / pk["hbm_gbs"], 4), "bound": "hbm"}
 
 
+def use_all_host_threads():
+    """The CPU legs use every core this process may run on: torchrun exports OMP_NUM_THREADS=1 to its workers,
+    which would otherwise leave the oracle on one thread."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def oracle_forward_fn(wl, ck):
     from oracle import vla_oracle as O
+    use_all_host_threads()
     w = {k: v.cpu() for k, v in ck.items()}
     images, state, noise = [t.cpu() for t in inputs(wl, "cpu")]
     if wl.get("batch", 1) > 1:      # the oracle has no batch dimension: one observation of the batch per step
