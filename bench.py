@@ -37,6 +37,8 @@ WORKLOADS = {
     "pi05_3v": dict(model="pi05", num_views=3, prompt_len=20, chunk=50, seed=1),
     # action expert alone over a prefilled K/V cache (the weight-streaming stage): stage mask 4 of the forward
     "cfg4": dict(model="pi0", num_views=3, prompt_len=20, chunk=50, seed=0, stages=4),
+    # throughput mode for Pi05: 32 observations per forward sharing one prompt
+    "pi05_b32": dict(model="pi05", num_views=2, prompt_len=52, chunk=50, seed=1, batch=32),
     # throughput mode: 32 independent observations per forward on each GPU
     "cfg5": dict(model="pi0", num_views=2, prompt_len=20, chunk=50, seed=0, batch=32),
 }
@@ -44,7 +46,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from the ncu
 # capture summarised under profiles/), keyed by workload; None until a capture exists.
-NCU_TRAFFIC_BYTES = {"cfg2": 144486144, "cfg1": None, "cfg3": None, "cfg4": None, "cfg5": None, "pi05_3v": None}   # profiles/gemm_sm100_geglu_prefix_p788.md
+NCU_TRAFFIC_BYTES = {"cfg2": 144486144, "cfg1": None, "cfg3": None, "cfg4": None, "cfg5": None, "pi05_3v": None, "pi05_b32": None}   # profiles/gemm_sm100_geglu_prefix_p788.md
 
 
 def peaks():
@@ -448,7 +450,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--batch", type=int, default=0, help="override the observations per forward of a Pi0 workload (throughput mode)")
+    ap.add_argument("--batch", type=int, default=0, help="override the observations per forward of a workload (throughput mode)")
     ap.add_argument("--mode", default="replicas", choices=["replicas", "latency"],
                     help="replicas: every rank runs whole forwards (default); latency: one observation, one SigLIP tower "
                          "per rank + gather (needs at least num_views ranks)")
@@ -521,7 +523,8 @@ def main():
     else:
         from pi05_infer import Pi05Inference
         ck = fast_checkpoint("pi05", wl["prompt_len"], wl["seed"], device)
-        infer = Pi05Inference(ck, wl["num_views"], wl["chunk"], discrete_state_input=False, device=local, flags=args.flags)
+        infer = Pi05Inference(ck, wl["num_views"], wl["chunk"], discrete_state_input=False, device=local, flags=args.flags,
+                              batch=wl.get("batch", 1))
         images, state, noise = inputs(wl, device)
         step = lambda: infer.forward(images, noise)
         host_args = [t.cpu().pin_memory() for t in (images, noise)]

@@ -51,11 +51,14 @@ class Pi05Inference:
     embedding (table[ids] * sqrt(2048), bf16) runs inside the captured graph.  The prompt window is
     max_prompt_len tokens and shorter prompts are masked by their valid length.  Callers that tokenise
     themselves pass forward(..., token_ids=ids) and may leave tokenizer_path=None.
+
+    batch (not in the reference): independent observations per forward, inputs then carry a leading batch
+    dimension; all observations of one call share the prompt.
     """
 
     def __init__(self, checkpoint, num_views, chunk_size, tokenizer_path=None, max_tokenize_len=200,
                  discrete_state_input=True, max_prompt_text=None, state_dim_for_max_prompt=None, *,
-                 device=None, n_vit_layers=0, n_layers=0, n_steps=0, flags=0, max_prompt_len=None):
+                 batch=1, device=None, n_vit_layers=0, n_layers=0, n_steps=0, flags=0, max_prompt_len=None):
         self.discrete_state_input = discrete_state_input
         self.tokenizer_path = tokenizer_path
         self.checkpoint = checkpoint
@@ -83,7 +86,7 @@ class Pi05Inference:
             if "embedding_weight" not in checkpoint:
                 raise KeyError("checkpoint must contain 'embedding_weight' when discrete_state_input=True")
             shapes["embedding_weight"] = tuple(checkpoint["embedding_weight"].shape)
-        self._engine = Engine(_capi.VLA_PI05, num_views, chunk_size, self.max_prompt_len, shapes, device=device,
+        self._engine = Engine(_capi.VLA_PI05, num_views, chunk_size, self.max_prompt_len, shapes, batch=batch, device=device,
                               n_vit_layers=n_vit_layers, n_layers=n_layers, n_steps=n_steps, flags=flags)
         for k, v in checkpoint.items():
             if k == "embedding_weight" and not discrete_state_input:
@@ -93,10 +96,11 @@ class Pi05Inference:
         self._language_embeds = checkpoint["language_embeds"]
         self.encoder_seq_len = num_views * 256 + self.max_prompt_len
         self._engine.finalize()
+        lead = (batch,) if batch > 1 else ()
         self.buffers = {
             "observation_images_normalized": self._engine.buffer("observation_images_normalized",
-                                                                 (num_views, 224, 224, 3)),
-            "diffusion_noise": self._engine.buffer("diffusion_noise", (chunk_size, 32)),
+                                                                 lead + (num_views, 224, 224, 3)),
+            "diffusion_noise": self._engine.buffer("diffusion_noise", lead + (chunk_size, 32)),
         }
 
     def estimate_max_prompt_len(self, tokenizer, task_prompt, state_dim, max_tokenize_len=200, state_token_value=255):

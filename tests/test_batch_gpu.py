@@ -33,3 +33,33 @@ def test_pi0_batch_matches_single_observation_oracle():
         err = (out[b].float() - want).abs()
         print("observation %d: max-abs %.3e mean-abs %.3e" % (b, err.max().item(), err.mean().item()))
         assert err.max().item() <= 2e-2 and err.mean().item() <= 3e-3
+
+
+def test_pi05_batch_shared_prompt():
+    """Pi05 in throughput mode: several observations per call, one prompt for all of them (shorter than the prompt
+    window, so the valid-length mask and the suffix RoPE start are exercised for every group)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from pi05_infer import Pi05Inference
+    d = torch.device("cuda")
+    B, nv, n_prompt, window = 4, 1, 9, 14
+    ck = synth.make_checkpoint("pi05", seed=1, prompt_ids=synth.prompt_ids(n_prompt, 2), n_vit_layers=2, n_layers=3)
+    ins = [synth.make_inputs(nv, 50, 10 + s) for s in range(B)]
+    images = torch.stack([i[0] for i in ins])
+    noise = torch.stack([i[2] for i in ins])
+    infer = Pi05Inference(ck, nv, 50, discrete_state_input=False, batch=B, n_vit_layers=2, n_layers=3, n_steps=2,
+                          max_prompt_len=window)
+    out = infer.forward(images, noise).clone()
+    torch.cuda.synchronize()
+    assert tuple(out.shape) == (B, 50, 32)
+    assert infer._engine.status_word() == 0
+    w = {k: v.to(d).float() for k, v in ck.items()}
+    pad = torch.zeros(window - n_prompt, 2048, device=d)
+    for b in range(B):
+        vx = O.vision_encoder(w, images[b].to(d).float(), n_layers=2)
+        enc = torch.cat([O.project_vision(w, vx), w["language_embeds"], pad], 0)
+        K, V = O.prefix_encoder(w, enc, valid_len=256 * nv + n_prompt, n_layers=3)
+        want = O.pi05_decoder(w, K, V, noise[b].to(d).float(), 256 * nv + n_prompt, n_layers=3, n_steps=2)
+        err = (out[b].float() - want).abs()
+        print("observation %d: max-abs %.3e mean-abs %.3e" % (b, err.max().item(), err.mean().item()))
+        assert err.max().item() <= 2e-2 and err.mean().item() <= 3e-3
