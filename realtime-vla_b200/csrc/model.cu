@@ -186,9 +186,13 @@ void pick_tiling(int tokens, int feat_tiles, int k_blocks, bool dual, int sm_cou
         const double load = kb * (16384.0 * accs + 128.0 * b) / 64.0;
         const double mma = kb * 2.0 * b * accs;
         const double epi = 22.0 * (b / 2) * accs;
-        const double exch = s > 1 ? 5000.0 * (b / 128) * accs : 0.0;     // partial tile through L2 + cluster barrier
+        // partial tile through L2 + cluster barrier; measured cheaper than twice the 128-token figure for a 4-way
+        // split of 256-token tiles (SigLIP down projection at 768 tokens: 22.7 us against 25.9 us for 128 x 2)
+        const double exch = s > 1 ? 5000.0 * (b == 256 ? (s == 4 ? 1.5 : 2.0) : 1.0) * accs : 0.0;
         const double cta = (load > mma ? load : mma) + epi + exch;
-        const int resident = s == 8 ? 128 : (s == 4 ? 144 : sm_count);  // clusters are scheduled whole within a GPC
+        // clusters are scheduled whole within a GPC: 144 CTAs in clusters of 4 measured like two waves
+        // (512 x 4304 x 1152: 29 us against 25 us for 72 CTAs), so 4- and 8-CTA clusters count 128 resident CTAs
+        const int resident = s >= 4 ? 128 : sm_count;
         const double waves = (double)((ctas + resident - 1) / resident);
         const double cost = waves * cta;
         if (cost < best) { best = cost; *bn = b; *split = s; *m256 = pair; }
