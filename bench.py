@@ -46,7 +46,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from the ncu
 # capture summarised under profiles/), keyed by workload; None until a capture exists.
-NCU_TRAFFIC_BYTES = {"cfg2": 144486144, "cfg1": None, "cfg3": None, "cfg4": None, "cfg5": None, "pi05_3v": None, "pi05_b32": None}   # profiles/gemm_sm100_geglu_prefix_p788.md
+NCU_TRAFFIC_BYTES = {"cfg2": 144519168, "cfg1": None, "cfg3": None, "cfg4": None, "cfg5": None, "pi05_3v": None, "pi05_b32": None}   # profiles/gemm_sm100_geglu_prefix_p788.md
 
 
 def peaks():
