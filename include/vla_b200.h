@@ -52,7 +52,9 @@ typedef struct vla_config {
   int n_steps;        /* 0 -> 10 */
   int flags;          /* bit 0: disable programmatic dependent launch; bit 1: run without a CUDA graph;
                          bit 2: SigLIP attention on the legacy mma.sync kernel instead of tcgen05;
-                         bit 3: prefix / suffix attention of batched forwards on the legacy mma.sync kernel */
+                         bit 3: prefix / suffix attention of batched forwards on the legacy mma.sync kernel;
+                         bit 4: action expert as per-operator launches instead of the persistent kernel (which serves
+                                single-observation handles with at most 52 suffix tokens) */
 } vla_config;
 
 /* Replaces Pi0Inference.__init__ / Pi05Inference.__init__ up to buffer allocation (pi0_infer.py:1245-1317). */
@@ -71,16 +73,19 @@ int vla_finalize(vla_handle h);
 
 /* Pi05 per-call prompt (pi05_infer.py:819-822): copies `len` rows of bf16 [len,2048] prompt embeddings
  * (host or device) into the prompt window, sets the valid prefix length and the suffix RoPE start
- * (num_views*256 + len - 1).  For Pi0 it only replaces the prompt rows (len must equal prompt_len). */
-int vla_set_prompt(vla_handle h, const void* embeds_bf16, int len);
+ * (num_views*256 + len - 1).  For Pi0 it only replaces the prompt rows (len must equal prompt_len).
+ * The updates are enqueued on `stream` (a cudaStream_t), like the reference's fill_/copy_ on the current stream:
+ * pass the stream the forwards run on and they are ordered between the previous forward and the next. */
+int vla_set_prompt(vla_handle h, const void* embeds_bf16, int len, void* stream);
 
 /* Pi05 per-call prompt from token ids (pi05_infer.py:769-785: embedding(ids) * sqrt(2048) in bf16, then the
  * copy into encoder_x, pi05_infer.py:819-822).  Needs the token table loaded with vla_load_weight under the key
  * 'embedding_weight' ((vocab, 2048), the reference's optional checkpoint entry, pi05_infer.py:726-743) BEFORE
  * vla_finalize: the gather then runs inside the captured graph and this call only copies `len` int32 ids (host or
  * device memory) and three scalars.  Ids outside the table are clamped and raise the device status word.
- * The tokenizer stays with the caller.  For Pi0 len must equal prompt_len. */
-int vla_set_prompt_ids(vla_handle h, const int32_t* ids, int len);
+ * The tokenizer stays with the caller.  For Pi0 len must equal prompt_len.  Enqueued on `stream` like vla_set_prompt;
+ * host ids may be reused as soon as the call returns. */
+int vla_set_prompt_ids(vla_handle h, const int32_t* ids, int len, void* stream);
 
 /* Device address and size of a named library-owned buffer, so that a host framework can wrap it without a
  * copy: "observation_images_normalized" bf16 (batch,nv,224,224,3), "observation_state_normalized" bf16
@@ -90,7 +95,9 @@ int vla_set_prompt_ids(vla_handle h, const int32_t* ids, int len);
 int vla_buffer(vla_handle h, const char* name, void** dev_ptr, size_t* bytes);
 
 /* Replaces infer_graph.replay() (pi0_infer.py:1360): runs the forward on `stream` (a cudaStream_t, NULL =
- * default stream) over the library-owned I/O buffers.  Asynchronous; the caller synchronises. */
+ * default stream) over the library-owned I/O buffers.  Asynchronous; the caller synchronises, and a caller that
+ * wants to know about device-side trouble reads vla_status_word after synchronising (the reference has no such
+ * check; vla_forward_host does it for its callers). */
 int vla_forward(vla_handle h, void* stream);
 
 /* Runs a subset of the forward: stage_mask is a combination of 1 = vision towers + projector into the prefix
@@ -102,7 +109,8 @@ int vla_forward_stages(vla_handle h, int stage_mask, void* stream);
 
 /* Replaces Pi0Inference.forward / Pi05Inference.forward for a caller holding HOST memory
  * (pi0_infer.py:1356-1361): copies bf16 images/state/noise in, runs, copies the bf16 (batch,chunk,32)
- * actions out and synchronises.  `state` is ignored for Pi05 (may be NULL). */
+ * actions out and synchronises.  `state` is ignored for Pi05 (may be NULL).  Returns VLA_ERR_DEVICE (and clears the
+ * word) when the device status word was raised during the call: the actions are then not to be trusted. */
 int vla_forward_host(vla_handle h, const void* images, const void* state, const void* noise, void* actions_out);
 
 /* ---- the steps either side of the forward in a robot loop -----------------------------------------------
@@ -131,8 +139,10 @@ int vla_preprocess_state(vla_handle h, int obs, const double* state, const doubl
 int vla_postprocess_actions(vla_handle h, int obs, const double* a, const double* b, int n_stats, int mode,
                             const double* state_raw, int n_state, int action_dim, double* out, void* stream);
 
-/* Device status word: OR of bounded-wait timeouts / shape violations seen by any kernel (0 = clean). */
+/* Device status word: OR of bounded-wait timeouts (bit 0) / shape violations such as a clamped token id (bit 1) seen by
+ * any kernel since the last clear (0 = clean).  Synchronises the device. */
 int vla_status_word(vla_handle h, int* out);
+int vla_clear_status(vla_handle h);
 
 /* Number of kernel launches in one forward, and device bytes held. */
 int vla_stats(vla_handle h, int* n_kernels, size_t* device_bytes);
@@ -142,6 +152,13 @@ int vla_stage_kernels(vla_handle h, int* n3);
 
 /* Per-stage device time of one forward (ms, CUDA events, outside the graph): vision, prefix, decoder. */
 int vla_time_stages(vla_handle h, float* ms3);
+
+/* Timeline of the persistent action-expert kernel (diagnostic, no counterpart in the reference): runs the expert
+ * stage once and returns, for every grid barrier of the kernel in order, the time CTA 0 arrived at it and the time
+ * it was released (out[2 i], out[2 i + 1], nanoseconds of the GPU's global timer).  The phases per Euler step are:
+ * action in-projection, (Pi0) action MLP, then per layer QKV, attention, attention merge, attention-out, GeGLU,
+ * down, and finally the out-projection with the Euler update.  *n_written = entries stored (<= max_entries). */
+int vla_expert_timeline(vla_handle h, unsigned long long* out, int max_entries, int* n_written);
 
 int vla_destroy(vla_handle h);
 const char* vla_last_error(vla_handle h);
@@ -208,6 +225,11 @@ int vla_op_vit_attention_tc(const void* qkv, void* o, int views, float scale, in
  *     e.g. more than 128 CTAs of a 64-token tile) are rejected with VLA_ERR_LIMIT.
  *   - The first call on each device looks up the scratch address and sets kernel attributes; make that call
  *     before any stream capture.  Later calls only enqueue the kernel on `stream` (asynchronous).
+ *   - split = 0 lets the library choose and then halves its choice until the partial tiles fit the 4 MiB (an unsplit
+ *     launch needs none); only an explicit split that does not fit is refused.
+ *   - A bounded wait inside the kernel that runs out cannot be reported by this asynchronous call: it sets a status
+ *     word that also lives in the library image; vla_op_gemm_noalloc_status (synchronising, allocation-free) returns
+ *     and clears it.  Non-zero means the output of an earlier call on this device is not to be trusted.
  *   - All calls share the one scratch array: calls that can overlap on the GPU (different streams) race on it.
  *     Calls on one stream are safe.  Nothing needs clearing between calls: every scratch element a call reads
  *     was written earlier by the same call.  split: 0 = heuristic, else 1, 2, 4 or 8. */
@@ -219,6 +241,7 @@ typedef struct vla_gemm_noalloc_desc {
   int split;
 } vla_gemm_noalloc_desc;
 int vla_op_gemm_noalloc(const vla_gemm_noalloc_desc* d, void* stream);
+int vla_op_gemm_noalloc_status(int* out);
 
 /* y bf16 [rows,D] = norm(x fp32 [rows,D]); mode 0 LayerNorm (w,b), 1 RMS, 2 adaRMS (w = style[3*D]); D 1024|1152|2048. */
 int vla_op_norm(const float* x, void* y, int rows, int D, int mode, const float* w, const float* b, void* stream);

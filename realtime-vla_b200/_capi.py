@@ -56,14 +56,14 @@ EXPORTS = {
     "vla_create": (C.c_int, [C.POINTER(VlaConfig), C.POINTER(C.c_void_p)]),
     "vla_load_weight": (C.c_int, [C.c_void_p, C.c_char_p, C.c_void_p, C.POINTER(C.c_int64), C.c_int, C.c_int]),
     "vla_finalize": (C.c_int, [C.c_void_p]),
-    "vla_set_prompt": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int]),
+    "vla_set_prompt": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "vla_buffer": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p), C.POINTER(C.c_size_t)]),
     "vla_forward": (C.c_int, [C.c_void_p, C.c_void_p]),
     "vla_forward_stages": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "vla_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "vla_status_word": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
     "vla_stats": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_size_t)]),
-    "vla_set_prompt_ids": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int]),
+    "vla_set_prompt_ids": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "vla_op_vit_attention_tc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_float, C.c_int, C.POINTER(C.c_float), C.c_void_p]),
     "vla_preprocess_image": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "vla_preprocess_state": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double),
@@ -76,6 +76,9 @@ EXPORTS = {
     "vla_last_error": (C.c_char_p, [C.c_void_p]),
     "vla_op_gemm": (C.c_int, [C.POINTER(GemmDesc), C.c_void_p]),
     "vla_op_gemm_noalloc": (C.c_int, [C.POINTER(GemmNoAllocDesc), C.c_void_p]),
+    "vla_op_gemm_noalloc_status": (C.c_int, [C.POINTER(C.c_int)]),
+    "vla_clear_status": (C.c_int, [C.c_void_p]),
+    "vla_expert_timeline": (C.c_int, [C.c_void_p, C.POINTER(C.c_ulonglong), C.c_int, C.POINTER(C.c_int)]),
     "vla_op_attention": (C.c_int, [C.POINTER(AttnDesc), C.c_void_p]),
     "vla_op_attention_tc": (C.c_int, [C.POINTER(AttnTcDesc), C.c_void_p]),
     "vla_op_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),

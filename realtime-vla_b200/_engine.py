@@ -107,13 +107,21 @@ class Engine:
         return raw.view(dtype).view(shape)
 
     def set_prompt(self, embeds):
+        """Prompt rows as embeddings; enqueued on the current stream, like the forward that follows."""
         embeds = embeds.detach().to(device=self.device, dtype=torch.bfloat16).contiguous()
-        _capi.check(self.lib.vla_set_prompt(self.handle, C.c_void_p(embeds.data_ptr()), embeds.shape[0]), self.handle)
+        stream = torch.cuda.current_stream(self.device)
+        _capi.check(self.lib.vla_set_prompt(self.handle, C.c_void_p(embeds.data_ptr()), embeds.shape[0],
+                                            C.c_void_p(stream.cuda_stream)), self.handle)
+        embeds.record_stream(stream)   # the copy may still be reading the rows when this tensor is released
 
     def set_prompt_ids(self, ids):
         """Prompt as token ids (int, host or device): embedded on the device from 'embedding_weight', inside the graph."""
         ids = torch.as_tensor(ids).detach().to(torch.int32).contiguous()
-        _capi.check(self.lib.vla_set_prompt_ids(self.handle, C.c_void_p(ids.data_ptr()), int(ids.numel())), self.handle)
+        stream = torch.cuda.current_stream(self.device)
+        _capi.check(self.lib.vla_set_prompt_ids(self.handle, C.c_void_p(ids.data_ptr()), int(ids.numel()),
+                                                C.c_void_p(stream.cuda_stream)), self.handle)
+        if ids.is_cuda:
+            ids.record_stream(stream)
 
     # ---- the steps either side of the forward (the reference's evaluation script does them with PIL / numpy) ----
     def preprocess_image(self, view, frame, obs=0):
@@ -176,6 +184,16 @@ class Engine:
         w = C.c_int()
         _capi.check(self.lib.vla_status_word(self.handle, C.byref(w)), self.handle)
         return w.value
+
+    def clear_status(self):
+        _capi.check(self.lib.vla_clear_status(self.handle), self.handle)
+
+    def expert_timeline(self):
+        """(arrive_ns, release_ns) of CTA 0 at every grid barrier of the persistent action-expert kernel."""
+        buf = (C.c_ulonglong * 4096)()
+        n = C.c_int()
+        _capi.check(self.lib.vla_expert_timeline(self.handle, buf, 4096, C.byref(n)), self.handle)
+        return [(buf[2 * i], buf[2 * i + 1]) for i in range(n.value // 2)]
 
     def stats(self):
         n, b = C.c_int(), C.c_size_t()

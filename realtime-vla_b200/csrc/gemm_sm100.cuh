@@ -165,16 +165,9 @@ __device__ __forceinline__ void gemm_epilogue_cols(const GemmEpi& e, const EpiTh
     }
     bf16* o = e.out + (size_t)t0 * e.ld_out + n;
     const size_t step = (size_t)tstride * e.ld_out;
-#if defined(VLA_EPI_EXPERIMENT) && VLA_EPI_EXPERIMENT == 1
-    float acc_ = 0.f;
-#pragma unroll
-    for (int j = 0; j < NC; ++j) acc_ += x[j];
-    if (n_valid > 0) o[0] = __float2bfloat16(acc_);
-#else
 #pragma unroll
     for (int j = 0; j < NC; ++j)
       if (j < n_valid) o[j * step] = __float2bfloat16(x[j]);
-#endif
   } else if (e.kind == EPI_RESID) {
     // Row bookkeeping without per-column integer division (an emulated division per column made this epilogue
     // 3x slower than its memory traffic): one division for the first column, then incremental wrap-around.

@@ -13,6 +13,8 @@
 #include <cstring>
 #include <functional>
 #include <map>
+#include <mutex>
+#include <set>
 #include <string>
 #include <vector>
 
@@ -21,12 +23,17 @@
 #include "attention_tc.cuh"
 #include "attention_vit_tc.cuh"
 #include "elementwise.cuh"
+#include "expert_persistent.cuh"
 #include "gemm_sm100.cuh"
 #include "preprocess.cuh"
 
 namespace {
 
 thread_local std::string g_last_error;
+
+// The persistent action-expert kernel serves eligible handles by default when true; flags bit 5 selects it
+// explicitly, bit 4 refuses it.
+constexpr bool XP_DEFAULT_ON = false;
 
 // ---------------------------------------------------------------------------------------------------
 // driver entry point for tensor-map encoding (no link-time dependency on libcuda)
@@ -118,6 +125,21 @@ cudaError_t launch_ex(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
+// The dynamic shared-memory opt-in of a kernel applies to the CURRENT device only, so it is remembered per
+// (device, kernel): a process may hold handles on several GPUs.
+cudaError_t ensure_smem_attr(const void* func, int bytes) {
+  static std::mutex mu;
+  static std::set<std::pair<int, const void*>> done;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.count({dev, func})) return cudaSuccess;
+  e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) done.insert({dev, func});
+  return e;
+}
+
 // ---------------------------------------------------------------------------------------------------
 // GEMM launch plan
 struct GemmOp {
@@ -205,13 +227,8 @@ template <int BN, bool DUAL, bool SPLITK, bool PAIR = false>
 cudaError_t launch_gemm_t(const GemmOp& op, cudaStream_t st, bool pdl) {
   using C = GemmCfg<BN, DUAL || PAIR, SPLITK>;
   static_assert(C::VALID, "tile shape leaves fewer than 3 pipeline stages");
-  static bool attr_set = false;
   auto kern = gemm_sm100_kernel<BN, DUAL, SPLITK, PAIR>;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    attr_set = true;
-  }
+  if (cudaError_t e = ensure_smem_attr(reinterpret_cast<const void*>(kern), C::SMEM_BYTES); e != cudaSuccess) return e;
   return launch_ex(kern, op.grid, dim3(GEMM_THREADS), C::SMEM_BYTES, st, op.p.split, pdl, op.p);
 }
 
@@ -307,13 +324,8 @@ bool build_gemm(GemmOp* op, const bf16* w, const bf16* w2, int n_feat, int n_fea
 // ---------------------------------------------------------------------------------------------------
 template <int HD>
 cudaError_t launch_attn_t(const AttnParams& p, int groups, cudaStream_t st, bool pdl) {
-  static bool attr_set = false;
   auto kern = attention_kernel<HD>;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<HD>::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    attr_set = true;
-  }
+  if (cudaError_t e = ensure_smem_attr(reinterpret_cast<const void*>(kern), AttnCfg<HD>::SMEM_BYTES); e != cudaSuccess) return e;
   dim3 grid(p.ksplit, (p.n_q + 63) / 64, groups);
   return launch_ex(kern, grid, dim3(128), AttnCfg<HD>::SMEM_BYTES, st, p.ksplit, pdl, p);
 }
@@ -367,23 +379,13 @@ bool build_attn_tc(AttnTcOp* op, const bf16* q, const bf16* k, int k_rows, const
   return true;
 }
 cudaError_t launch_attn_tc(const AttnTcOp& op, cudaStream_t st, bool pdl) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnTcCfg::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    attr_set = true;
-  }
+  if (cudaError_t e = ensure_smem_attr(reinterpret_cast<const void*>(attention_tc_kernel), AttnTcCfg::SMEM_BYTES); e != cudaSuccess) return e;
   return launch_ex(attention_tc_kernel, op.grid, dim3(AttnTcCfg::THREADS), AttnTcCfg::SMEM_BYTES, st, op.p.ksplit, pdl, op.p);
 }
 
 // SigLIP attention of `views` camera views (16 heads x 72, 256 tokens each) on tcgen05
 cudaError_t launch_vit_attn_tc(const VitAttnTcParams& p, int views, cudaStream_t st, bool pdl) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(vit_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, VitAttnTcCfg::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    attr_set = true;
-  }
+  if (cudaError_t e = ensure_smem_attr(reinterpret_cast<const void*>(vit_attention_tc_kernel), VitAttnTcCfg::SMEM_BYTES); e != cudaSuccess) return e;
   return launch_ex(vit_attention_tc_kernel, dim3(2, 16, views), dim3(VitAttnTcCfg::THREADS), VitAttnTcCfg::SMEM_BYTES, st, 1, pdl, p);
 }
 
@@ -456,6 +458,9 @@ struct vla_model {
   int vocab = 0;
   int *d_ids = nullptr, *d_n_ids = nullptr;   // prompt token ids and their count (-1: prompt given as embeddings)
   int n_ids = -1;
+  int* h_scalars = nullptr;       // pinned staging slots for the per-call scalars (64 x 3 ints)
+  unsigned scalar_slot = 0;
+  int* h_status = nullptr;        // pinned copy of the device status word read by vla_forward_host
   // pre/post-processing: resample tables per (input size, output size), frame staging that grows on demand
   struct ResampleTable { int ksize; int* bounds; int* kk; };
   std::map<std::pair<int, int>, ResampleTable> resample;
@@ -467,6 +472,14 @@ struct vla_model {
   size_t gemm_scratch_cap = 0;    // floats
   float* attn_scratch;            // key-split partial outputs of whichever attention kernel is running
   size_t attn_scratch_cap = 0;
+  // persistent action-expert kernel (single observation): per-CTA weight streams and its small exchange buffers
+  bool use_xp = false;
+  int xp_G = 0, xp_chunks = 0;
+  uint4* xp_stream = nullptr;
+  float *xp_ssq = nullptr, *xp_part = nullptr, *xp_stat = nullptr, *xp_sw_fin = nullptr;
+  unsigned int* xp_sync = nullptr;
+  unsigned long long* xp_trace = nullptr;
+  xp::Params xp_params;
 
   struct Op { int stage; bool is_kernel; std::function<cudaError_t(cudaStream_t)> fn; };
   std::vector<Op> ops;
@@ -617,23 +630,46 @@ bool alloc_buffers(vla_model* m) {
   ok &= m->dalloc(&m->decoder_xn, Ns * 1024);
   ok &= m->dalloc(&m->decoder_xb, Ns * 1024);
   ok &= m->dalloc(&m->decoder_ssq, (size_t)32 * Ns);
-  ok &= m->dalloc(&m->decoder_q, Ns * 2048);
-  ok &= m->dalloc(&m->decoder_attn, Ns * 2048);
-  ok &= m->dalloc(&m->decoder_hidden, Ns * 4096);
-  ok &= m->dalloc(&m->decoder_act, Nc * 1024);
+  ok &= m->dalloc(&m->decoder_q, Ns * 2048, "decoder_q");
+  ok &= m->dalloc(&m->decoder_attn, Ns * 2048, "decoder_attn");
+  ok &= m->dalloc(&m->decoder_hidden, Ns * 4096, "decoder_hidden");
+  ok &= m->dalloc(&m->decoder_act, Nc * 1024, "decoder_act");
   ok &= m->dalloc(&m->decoder_xfin, Nc * 1024);
   ok &= m->dalloc(&m->lang, (size_t)std::max(m->L, 1) * 2048, "language_embeds");
   ok &= m->dalloc(&m->rope_cos, (size_t)(m->T + 1) * 128);
   ok &= m->dalloc(&m->rope_sin, (size_t)(m->T + 1) * 128);
-  ok &= m->dalloc(&m->d_valid_len, 1);
-  ok &= m->dalloc(&m->d_pos_base, 1);
+  ok &= m->dalloc(&m->d_valid_len, 4);   // one block: valid length, suffix RoPE start, id count (uploaded together)
+  m->d_pos_base = m->d_valid_len + 1;
+  m->d_n_ids = m->d_valid_len + 2;
   ok &= m->dalloc(&m->d_status, 1);
   ok &= m->dalloc(&m->d_ids, (size_t)std::max(m->L, 1));
-  ok &= m->dalloc(&m->d_n_ids, 1);
   m->gemm_scratch_cap = (size_t)16 << 20;   // 64 MB: 176 CTAs x the largest partial tile (128 x 256 x 2 fp32)
   ok &= m->dalloc(&m->gemm_scratch, m->gemm_scratch_cap);
   m->attn_scratch_cap = (size_t)6 << 20;    // 24 MB: 176 CTAs x 64 rows x 260 fp32, with headroom
   ok &= m->dalloc(&m->attn_scratch, m->attn_scratch_cap);
+  // Persistent action-expert kernel: one observation, suffix rows that fit its shared-memory tile, enough SMs for
+  // the feature partition, key splits of at most ATT_MAX_KEYS keys (flags bit 4 keeps the per-operator launches).
+  m->use_xp = m->B == 1 && m->S <= xp::MAX_ROWS && m->sm_count >= xp::N_OWNERS && !(m->cfg.flags & 16) && (XP_DEFAULT_ON || (m->cfg.flags & 32));
+  if (m->use_xp) {
+    xp::Params& xq = m->xp_params;
+    memset(&xq, 0, sizeof xq);
+    m->xp_G = std::min(m->sm_count, 160);
+    xq.att_nrb = (m->S * 8 + xp::ATT_ROWS - 1) / xp::ATT_ROWS;
+    xq.att_ks = std::max(1, std::min(m->xp_G / xq.att_nrb, (m->T + 15) / 16));
+    xq.att_kps = round_up((m->T + xq.att_ks - 1) / xq.att_ks, 16);
+    if (xq.att_kps > xp::ATT_MAX_KEYS) m->use_xp = false;
+  }
+  if (m->use_xp) {
+    const size_t items = (size_t)m->xp_params.att_nrb * m->xp_params.att_ks;
+    m->xp_chunks = m->nl * xp::CH_PER_LAYER + 2;
+    ok &= m->dalloc(&m->xp_stream, (size_t)m->xp_G * m->xp_chunks * (xp::CHUNK_BYTES / 16));
+    ok &= m->dalloc(&m->xp_ssq, (size_t)xp::N_OWNERS * 64);
+    ok &= m->dalloc(&m->xp_part, items * xp::ATT_ROWS * 256);
+    ok &= m->dalloc(&m->xp_stat, items * xp::ATT_ROWS * 2);
+    ok &= m->dalloc(&m->xp_sync, 2);
+    ok &= m->dalloc(&m->xp_trace, 4096);
+    ok &= m->dalloc(&m->xp_sw_fin, (size_t)10 * 32);
+  }
   if (m->pi05) {
     ok &= m->dalloc(&m->style_attn, (size_t)m->nsteps * m->nl * 3072);
     ok &= m->dalloc(&m->style_ffn, (size_t)m->nsteps * m->nl * 3072);
@@ -836,8 +872,87 @@ void plan_prefix(Plan& pl) {
   }
 }
 
+// ---- persistent action-expert kernel ---------------------------------------------------------------
+// Repack the expert's weights (already K-major in W[...]) into the per-CTA streams the kernel reads.
+int xp_pack(vla_model* m) {
+  const int G = m->xp_G;
+  bf16* stream = reinterpret_cast<bf16*>(m->xp_stream);
+  const size_t chunk_elems = xp::CHUNK_BYTES / 2;
+  auto layer_w = [&](const char* key, int l) {
+    WEntry& e = m->W.at(key);
+    return e.w + (size_t)l * e.Np * e.Kp;
+  };
+  for (int l = 0; l < m->nl; ++l)
+    xp::pack_layer_kernel<<<dim3(xp::CH_PER_LAYER, G), 256>>>(layer_w("decoder_attn_qkv_w", l), layer_w("decoder_attn_o_w", l),
+                                                              layer_w("decoder_ffn_gate_w", l), layer_w("decoder_ffn_up_w", l),
+                                                              layer_w("decoder_ffn_down_w", l), l, m->xp_chunks, stream);
+  const int misc = m->nl * xp::CH_PER_LAYER;
+  if (!m->pi05)
+    for (int c = 0; c < xp::N_OWNERS; ++c)
+      xp::pack_chunk_kernel<<<32, 256>>>(m->W.at("decoder_action_mlp_w").w, 1024, 1024, 1024, 8 * c, 0,
+                                         stream + ((size_t)c * m->xp_chunks + misc) * chunk_elems);
+  const WEntry& wo = m->W.at(m->pi05 ? "decoder_action_out_proj_w" : "decoder_action_fused_out_proj_w");
+  for (int c = 0; c < 4; ++c)
+    xp::pack_chunk_kernel<<<32, 256>>>(wo.w, wo.Kp, 32, 1024, 8 * c, 0, stream + ((size_t)c * m->xp_chunks + misc + 1) * chunk_elems);
+  CK(cudaGetLastError());
+  CK(cudaDeviceSynchronize());
+  return VLA_OK;
+}
+
+cudaError_t launch_expert_persistent(vla_model* m, cudaStream_t st, unsigned long long* trace) {
+  auto kern = xp::expert_persistent_kernel;
+  if (cudaError_t e = ensure_smem_attr(reinterpret_cast<const void*>(kern), xp::SMEM_BYTES); e != cudaSuccess) return e;
+  // barrier counter and abort word start from zero at every launch
+  if (cudaError_t e = cudaMemsetAsync(m->xp_sync, 0, 2 * sizeof(unsigned int), st); e != cudaSuccess) return e;
+  xp::Params p = m->xp_params;
+  p.trace = trace;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = dim3(m->xp_G);
+  cfg.blockDim = dim3(xp::THREADS);
+  cfg.dynamicSmemBytes = xp::SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;   // all CTAs co-resident: they wait for one another at grid barriers
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+void plan_decoder_persistent(Plan& pl) {
+  vla_model* m = pl.m;
+  pl.stage = 2;
+  const bool pi05 = m->pi05;
+  xp::Params& p = m->xp_params;   // attention split already chosen in alloc_buffers
+  p.pi05 = pi05; p.S = m->S; p.C = m->C; p.P = m->P; p.T = m->T; p.nl = m->nl; p.nsteps = m->nsteps; p.G = m->xp_G;
+  p.wstream = m->xp_stream; p.chunks_per_cta = m->xp_chunks; p.misc_base = m->nl * xp::CH_PER_LAYER;
+  if (pi05) {
+    p.w_in = m->W.at("decoder_action_in_proj_w").w;
+    p.b_in = pl.vec("decoder_action_in_proj_b"); p.ld_b_in = 0;
+    p.b_out = pl.vec("decoder_action_out_proj_b");
+    p.sw_fin = m->xp_sw_fin;
+    p.style_attn = m->style_attn; p.style_ffn = m->style_ffn; p.style_fin = m->style_fin;
+    p.sw_qkv = m->sw_qkv; p.sw_gate = m->sw_gate; p.sw_up = m->sw_up;
+    p.valid_len_ptr = m->d_valid_len; p.pos_base_ptr = m->d_pos_base;
+  } else {
+    p.w_in = m->W.at("decoder_action_fused_in_proj_w").w;
+    p.b_in = pl.vec("decoder_action_fused_time_biases"); p.ld_b_in = m->W.at("decoder_action_fused_time_biases").Np;
+    p.b_mlp = pl.vec("decoder_action_mlp_b");
+    p.w_state = m->W.at("decoder_state_in_proj_w").w; p.b_state = pl.vec("decoder_state_in_proj_b"); p.state = m->state;
+    p.b_out = pl.vec("decoder_action_fused_out_proj_b");
+  }
+  p.noise = m->noise; p.noise_f32 = m->noise_f32; p.act = m->decoder_act; p.x_out = m->decoder_x; p.xb = m->decoder_xb;
+  p.ssq = m->xp_ssq; p.q = m->decoder_q; p.kcache = m->kcache; p.vcache = m->vcache; p.attn = m->decoder_attn;
+  p.hidden = m->decoder_hidden; p.att_part = m->xp_part; p.att_stat = m->xp_stat;
+  p.rope_cos = m->rope_cos; p.rope_sin = m->rope_sin;
+  p.bar_ctr = m->xp_sync; p.status = m->d_status; p.trace = nullptr;
+  pl.kernel([m](cudaStream_t st) { return launch_expert_persistent(m, st, nullptr); });
+}
+
 void plan_decoder(Plan& pl) {
   vla_model* m = pl.m;
+  if (m->use_xp) { plan_decoder_persistent(pl); return; }
   pl.stage = 2;
   const bool pdl = m->use_pdl, pi05 = m->pi05;
   const int Ns = m->B * m->S, Nc = m->B * m->C, B = m->B, S = m->S, C = m->C;
@@ -984,6 +1099,11 @@ int pi05_precompute(vla_model* m, cudaStream_t st) {
       b.outf = m->sw_up + (size_t)l * 4096;
       pl.gemm("decoder_ffn_up_w", nullptr, l, m->shift_ffn_bf + (size_t)l * ns * 1024, ns, 1024, 1024, b);
     }
+  }
+  if (m->use_xp) {   // shift @ W of the final adaRMS norm, folded into the out-projection of the persistent kernel
+    const float* sf = m->style_fin; const bf16* wo = m->W.at("decoder_action_out_proj_w").w; const int kp = m->W.at("decoder_action_out_proj_w").Kp;
+    float* out = m->xp_sw_fin;
+    pl.kernel([=](cudaStream_t st2) { xp::sw_fin_kernel<<<ns, 1024, 0, st2>>>(sf, wo, kp, ns, out); return cudaGetLastError(); });
   }
   int rc = VLA_OK;
   if (!pl.ok) rc = m->fail(VLA_ERR_CUDA, "pi05 precompute plan: %s", pl.err.c_str());
@@ -1155,38 +1275,44 @@ int vla_load_weight(vla_handle m, const char* key, const void* data, const int64
   return VLA_OK;
 }
 
-static int upload_scalars(vla_model* m) {
+// Every update below is enqueued on `st`, so it is ordered after a forward already running on that stream and
+// before the next one (the reference's fill_/copy_ are stream-ordered the same way, pi05_infer.py:819-822).  The
+// three scalars travel as one 12-byte copy from a pinned staging slot of the handle; slots rotate so that a slot is
+// not rewritten while an earlier copy may still be reading it.
+static int upload_scalars(vla_model* m, cudaStream_t st) {
   // Pi05: valid prefix length and suffix RoPE start (pi05_infer.py:787-790, 821); Pi0: fixed
-  const int valid = m->valid_len, pos_base = m->valid_len - 1;
-  CK(cudaMemcpy(m->d_valid_len, &valid, sizeof(int), cudaMemcpyHostToDevice));
-  CK(cudaMemcpy(m->d_pos_base, &pos_base, sizeof(int), cudaMemcpyHostToDevice));
-  CK(cudaMemcpy(m->d_n_ids, &m->n_ids, sizeof(int), cudaMemcpyHostToDevice));
+  if (!m->h_scalars) CK(cudaMallocHost(reinterpret_cast<void**>(&m->h_scalars), 64 * 3 * sizeof(int)));
+  int* slot = m->h_scalars + 3 * (m->scalar_slot++ & 63);
+  slot[0] = m->valid_len; slot[1] = m->valid_len - 1; slot[2] = m->n_ids;
+  CK(cudaMemcpyAsync(m->d_valid_len, slot, 3 * sizeof(int), cudaMemcpyHostToDevice, st));
   return VLA_OK;
 }
 
-int vla_set_prompt_ids(vla_handle m, const int32_t* ids, int len) {
+int vla_set_prompt_ids(vla_handle m, const int32_t* ids, int len, void* stream) {
   if (!m) return VLA_ERR_STATE;
   cudaSetDevice(m->cfg.device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (!m->embed_table) return m->fail(VLA_ERR_STATE, "vla_set_prompt_ids needs 'embedding_weight' loaded before vla_finalize");
   if (len < 0 || len > m->L) return m->fail(VLA_ERR_SHAPE, "prompt of %d tokens does not fit the window of %d", len, m->L);
   if (!m->pi05 && len != m->L) return m->fail(VLA_ERR_SHAPE, "Pi0 prompt length is fixed at %d", m->L);
   if (len > 0 && !ids) return m->fail(VLA_ERR_STATE, "null token ids");
-  if (len > 0) CK(cudaMemcpy(m->d_ids, ids, (size_t)len * sizeof(int32_t), cudaMemcpyDefault));
+  if (len > 0) CK(cudaMemcpyAsync(m->d_ids, ids, (size_t)len * sizeof(int32_t), cudaMemcpyDefault, st));
   m->n_ids = len;
   m->valid_len = m->nv * 256 + len;
-  return upload_scalars(m);
+  return upload_scalars(m, st);
 }
 
-int vla_set_prompt(vla_handle m, const void* embeds, int len) {
+int vla_set_prompt(vla_handle m, const void* embeds, int len, void* stream) {
   if (!m) return VLA_ERR_STATE;
   cudaSetDevice(m->cfg.device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (len < 0 || len > m->L) return m->fail(VLA_ERR_SHAPE, "prompt of %d rows does not fit the window of %d", len, m->L);
   if (!m->pi05 && len != m->L) return m->fail(VLA_ERR_SHAPE, "Pi0 prompt length is fixed at %d", m->L);
-  CK(cudaMemset(m->lang, 0, (size_t)std::max(m->L, 1) * 2048 * 2));
-  if (len > 0) CK(cudaMemcpy(m->lang, embeds, (size_t)len * 2048 * 2, cudaMemcpyDefault));
+  CK(cudaMemsetAsync(m->lang, 0, (size_t)std::max(m->L, 1) * 2048 * 2, st));
+  if (len > 0) CK(cudaMemcpyAsync(m->lang, embeds, (size_t)len * 2048 * 2, cudaMemcpyDefault, st));
   m->n_ids = -1;     // the prompt rows are embeddings: the id gather inside the graph stays idle
   m->valid_len = m->nv * 256 + len;
-  return upload_scalars(m);
+  return upload_scalars(m, st);
 }
 
 int vla_finalize(vla_handle m) {
@@ -1208,14 +1334,19 @@ int vla_finalize(vla_handle m) {
     CK(cudaMemcpy(m->rope_cos, c.data(), c.size() * 4, cudaMemcpyHostToDevice));
     CK(cudaMemcpy(m->rope_sin, s.data(), s.size() * 4, cudaMemcpyHostToDevice));
   }
-  int rc = upload_scalars(m);
+  int rc = upload_scalars(m, m->own_stream);
   if (rc) return rc;
+  CK(cudaStreamSynchronize(m->own_stream));
   if (m->pi05) {
     if (m->named.find("decoder_time_embeds") == m->named.end()) {
       bf16* dst = nullptr;
       if (!m->dalloc(&dst, (size_t)10 * 1024, "decoder_time_embeds")) return m->fail(VLA_ERR_CUDA, "allocation failed");
     }
     rc = pi05_precompute(m, m->own_stream);
+    if (rc) return rc;
+  }
+  if (m->use_xp) {
+    rc = xp_pack(m);
     if (rc) return rc;
   }
   Plan pl{m};
@@ -1253,6 +1384,7 @@ int vla_buffer(vla_handle m, const char* name, void** dev_ptr, size_t* bytes) {
 int vla_forward(vla_handle m, void* stream) {
   if (!m || !m->finalized) return m ? m->fail(VLA_ERR_STATE, "forward before finalize") : VLA_ERR_STATE;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  cudaSetDevice(m->cfg.device);
   if (m->use_graph) {
     CK(cudaGraphLaunch(m->graph_exec, st));
     return VLA_OK;
@@ -1303,7 +1435,15 @@ int vla_forward_host(vla_handle m, const void* images, const void* state, const 
   int rc = vla_forward(m, st);
   if (rc) return rc;
   CK(cudaMemcpyAsync(actions_out, m->noise, B * m->C * 32 * 2, cudaMemcpyDeviceToHost, st));
+  // the status word rides along: a bounded wait that ran out or a clamped token id must not pass silently
+  if (!m->h_status) CK(cudaMallocHost(reinterpret_cast<void**>(&m->h_status), sizeof(int)));
+  CK(cudaMemcpyAsync(m->h_status, m->d_status, sizeof(int), cudaMemcpyDeviceToHost, st));
   CK(cudaStreamSynchronize(st));
+  if (*m->h_status) {
+    const int w = *m->h_status;
+    cudaMemsetAsync(m->d_status, 0, sizeof(int), st);
+    return m->fail(VLA_ERR_DEVICE, "device status word 0x%x (bit 0: a bounded wait ran out, bit 1: bad shape / token id); cleared", w);
+  }
   return VLA_OK;
 }
 
@@ -1466,6 +1606,13 @@ int vla_status_word(vla_handle m, int* out) {
   return VLA_OK;
 }
 
+int vla_clear_status(vla_handle m) {
+  if (!m) return VLA_ERR_STATE;
+  cudaSetDevice(m->cfg.device);
+  CK(cudaMemset(m->d_status, 0, sizeof(int)));
+  return VLA_OK;
+}
+
 int vla_stats(vla_handle m, int* n_kernels, size_t* device_bytes) {
   if (!m) return VLA_ERR_STATE;
   if (n_kernels) *n_kernels = m->n_kernels;
@@ -1507,6 +1654,8 @@ int vla_destroy(vla_handle m) {
   for (auto& kv : m->stage_graphs) cudaGraphExecDestroy(kv.second);
   if (m->graph) cudaGraphDestroy(m->graph);
   if (m->own_stream) cudaStreamDestroy(m->own_stream);
+  if (m->h_scalars) cudaFreeHost(m->h_scalars);
+  if (m->h_status) cudaFreeHost(m->h_status);
   for (void* p : m->allocs) cudaFree(p);
   delete m;
   return VLA_OK;
@@ -1582,24 +1731,6 @@ int vla_op_gemm(const vla_gemm_desc* d, void* stream) {
     CKG(cudaMalloc(&scratch, gemm_scratch_floats(op.bn, op.dual, op.grid) * sizeof(float)));
     op.p.scratch = scratch;
   }
-#ifdef VLA_TRACE
-  {
-    long long* tr = nullptr;
-    CKG(cudaMalloc(&tr, 16 * sizeof(long long)));
-    CKG(cudaMemset(tr, 0, 16 * sizeof(long long)));
-    for (int rep = 0; rep < 3; ++rep) CKG(launch_gemm(op, st, false));   // warm: descriptors, code, L2
-    op.p.trace = tr;
-    CKG(launch_gemm(op, st, false));
-    op.p.trace = nullptr;
-    CKG(cudaStreamSynchronize(st));
-    long long h[16];
-    CKG(cudaMemcpy(h, tr, sizeof h, cudaMemcpyDeviceToHost));
-    cudaFree(tr);
-    printf("trace tokens=%d K=%d N=%d grid=(%d,%d,%d):", d->tokens, d->K, d->N, op.grid.x, op.grid.y, op.grid.z);
-    for (int i = 1; i < 14; ++i) printf(" t%d=%lld", i, h[i] ? h[i] - h[0] : -1);
-    printf("\n");
-  }
-#endif
   CKG(launch_gemm(op, st, false));
   CKG(cudaStreamSynchronize(st));
   if (d->iters > 0 && d->ms_per_iter) {
@@ -1676,6 +1807,9 @@ done:
 // every GPU that loads the library from load time until exit and no call ever has to allocate it.
 #define VLA_NOALLOC_SCRATCH_FLOATS (1u << 20)   /* 4 MiB */
 static __device__ __align__(256) float vla_noalloc_scratch[VLA_NOALLOC_SCRATCH_FLOATS];
+// Status word of the same entry point (a bounded wait inside the kernel that ran out sets bit 0): also part of the
+// library image, so reporting a timeout needs no allocation either.
+static __device__ int vla_noalloc_status;
 
 int vla_op_vit_attention_tc(const void* qkv, void* o, int views, float scale, int iters, float* ms_per_iter, void* stream) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -1689,24 +1823,6 @@ int vla_op_vit_attention_tc(const void* qkv, void* o, int views, float scale, in
   p.qkv = reinterpret_cast<const bf16*>(qkv); p.o = reinterpret_cast<bf16*>(o);
   p.scale_log2e = scale * 1.4426950408889634f; p.status = status; p.trace = nullptr;
   CKG(launch_vit_attn_tc(p, views, st, false));
-#ifdef VLA_TRACE
-  {
-    long long* tr = nullptr;
-    CKG(cudaMalloc(&tr, 16 * sizeof(long long)));
-    CKG(cudaMemset(tr, 0, 16 * sizeof(long long)));
-    for (int rep = 0; rep < 3; ++rep) CKG(launch_vit_attn_tc(p, views, st, false));
-    p.trace = tr;
-    CKG(launch_vit_attn_tc(p, views, st, false));
-    p.trace = nullptr;
-    CKG(cudaStreamSynchronize(st));
-    long long h[16];
-    CKG(cudaMemcpy(h, tr, sizeof h, cudaMemcpyDeviceToHost));
-    cudaFree(tr);
-    fprintf(stderr, "vit attention timeline (cycles after entry):");
-    for (int i = 1; i <= 8; ++i) fprintf(stderr, " %lld", h[i] - h[0]);
-    fprintf(stderr, "\n");
-  }
-#endif
   if (iters > 0 && ms_per_iter) {
     CKG(cudaEventCreate(&e0));
     CKG(cudaEventCreate(&e1));
@@ -1731,24 +1847,37 @@ done:
   return rc;
 }
 
+// per-device addresses of the two symbols above, looked up on the first call on that device
+struct NoallocDev { float* scratch = nullptr; int* status = nullptr; };
+static NoallocDev* noalloc_device(int* dev_out) {
+  // In host code the arrays' names are only handles for the runtime, not device addresses, so they must go through
+  // cudaGetSymbolAddress with the target device current; the result differs per device.
+  static NoallocDev table[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { g_last_error = "vla_op_gemm_noalloc: no current device"; return nullptr; }
+  NoallocDev& nd = table[dev];
+  if (!nd.scratch) {
+    float* ptr = nullptr;
+    int* sptr = nullptr;
+    cudaError_t ce = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), vla_noalloc_scratch);
+    if (ce == cudaSuccess) ce = cudaGetSymbolAddress(reinterpret_cast<void**>(&sptr), vla_noalloc_status);
+    if (ce != cudaSuccess || !ptr || !sptr) {
+      g_last_error = std::string("vla_op_gemm_noalloc: cudaGetSymbolAddress failed: ") + cudaGetErrorString(ce);
+      return nullptr;
+    }
+    nd.status = sptr;
+    nd.scratch = ptr;
+  }
+  if (dev_out) *dev_out = dev;
+  return &nd;
+}
+
 int vla_op_gemm_noalloc(const vla_gemm_noalloc_desc* d, void* stream) {
-  // Device address of the scratch array, looked up once per device.  In host code the array's name is only a
-  // handle for the runtime, not a device address, so it must go through cudaGetSymbolAddress with the target
-  // device current; the result differs per device.
-  static float* scratch_of_device[64] = {nullptr};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (!d || !d->x || !d->w_nk || !d->out_bf16) { g_last_error = "vla_op_gemm_noalloc: null argument"; return VLA_ERR_STATE; }
   int dev = 0, sms = 148;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { g_last_error = "vla_op_gemm_noalloc: no current device"; return VLA_ERR_CUDA; }
-  if (!scratch_of_device[dev]) {
-    float* ptr = nullptr;
-    cudaError_t ce = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), vla_noalloc_scratch);
-    if (ce != cudaSuccess || !ptr) {
-      g_last_error = std::string("vla_op_gemm_noalloc: cudaGetSymbolAddress failed: ") + cudaGetErrorString(ce);
-      return VLA_ERR_CUDA;
-    }
-    scratch_of_device[dev] = ptr;
-  }
+  NoallocDev* nd = noalloc_device(&dev);
+  if (!nd) return VLA_ERR_CUDA;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (d->K % 8) { g_last_error = "vla_op_gemm_noalloc: K must be a multiple of 8 (16-byte rows for TMA)"; return VLA_ERR_SHAPE; }
   if (d->k_pad % 64 || d->n_pad % 128 || d->k_pad < d->K || d->n_pad < d->N) {
@@ -1764,38 +1893,64 @@ int vla_op_gemm_noalloc(const vla_gemm_noalloc_desc* d, void* stream) {
   e.ld_out = d->N;
   GemmOp op;
   std::string err;
-  if (!build_gemm(&op, reinterpret_cast<const bf16*>(d->w_nk), nullptr, d->N, d->n_pad, d->k_pad,
-                  reinterpret_cast<const bf16*>(d->x), d->tokens, d->K, d->K, e, nullptr, sms, 0, d->split, &err, -1)) {
-    g_last_error = "vla_op_gemm_noalloc: " + err;
-    return VLA_ERR_SHAPE;
+  // split = 0: take the library's choice, then halve it until the partial tiles fit the built-in array (an unsplit
+  // launch needs none); an explicit split that does not fit is the caller's error
+  int split = d->split;
+  for (;;) {
+    if (!build_gemm(&op, reinterpret_cast<const bf16*>(d->w_nk), nullptr, d->N, d->n_pad, d->k_pad,
+                    reinterpret_cast<const bf16*>(d->x), d->tokens, d->K, d->K, e, nd->status, sms, 0, split, &err, -1)) {
+      g_last_error = "vla_op_gemm_noalloc: " + err;
+      return VLA_ERR_SHAPE;
+    }
+    if (gemm_scratch_floats(op.bn, op.dual, op.grid) <= VLA_NOALLOC_SCRATCH_FLOATS) break;
+    if (d->split != 0 || op.p.split <= 1) {
+      char buf[200];
+      snprintf(buf, sizeof buf, "vla_op_gemm_noalloc: this shape needs %zu scratch floats, the built-in scratch holds %u; "
+               "use a smaller split or vla_op_gemm", gemm_scratch_floats(op.bn, op.dual, op.grid), VLA_NOALLOC_SCRATCH_FLOATS);
+      g_last_error = buf;
+      return VLA_ERR_LIMIT;
+    }
+    split = op.p.split / 2;
   }
-  const size_t need = gemm_scratch_floats(op.bn, op.dual, op.grid);
-  if (need > VLA_NOALLOC_SCRATCH_FLOATS) {
-    char buf[200];
-    snprintf(buf, sizeof buf, "vla_op_gemm_noalloc: this shape needs %zu scratch floats, the built-in scratch holds %u; "
-             "use a smaller split or vla_op_gemm", need, VLA_NOALLOC_SCRATCH_FLOATS);
-    g_last_error = buf;
-    return VLA_ERR_LIMIT;
-  }
-  op.p.scratch = scratch_of_device[dev];
+  op.p.scratch = nd->scratch;
   cudaError_t ce = launch_gemm(op, st, false);
   if (ce != cudaSuccess) { g_last_error = std::string("vla_op_gemm_noalloc: launch failed: ") + cudaGetErrorString(ce); return VLA_ERR_CUDA; }
   return VLA_OK;
 }
 
-#ifdef VLA_TRACE
-// development only: copy out and reset the cross-kernel timeline
-int vla_ktrace_dump(unsigned long long* out, int max_records) {
-  unsigned int n = 0;
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(&n, vla_ktrace_n, sizeof n);
-  if ((int)n > max_records) n = max_records;
-  cudaMemcpyFromSymbol(out, vla_ktrace, (size_t)n * 16);
-  unsigned int zero = 0;
-  cudaMemcpyToSymbol(vla_ktrace_n, &zero, sizeof zero);
-  return (int)n;
+int vla_op_gemm_noalloc_status(int* out) {
+  if (!out) return VLA_ERR_STATE;
+  NoallocDev* nd = noalloc_device(nullptr);
+  if (!nd) return VLA_ERR_CUDA;
+  int zero = 0;
+  // both copies synchronise with the device; neither allocates
+  if (cudaMemcpy(out, nd->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess ||
+      cudaMemcpy(nd->status, &zero, sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess) {
+    g_last_error = std::string("vla_op_gemm_noalloc_status: ") + cudaGetErrorString(cudaGetLastError());
+    return VLA_ERR_CUDA;
+  }
+  return VLA_OK;
 }
+
+// Timeline of the persistent action-expert kernel: one run of the expert stage on the handle's own stream with
+// CTA 0 recording %globaltimer at every grid barrier (arrival, release).  out[2 i], out[2 i + 1] in nanoseconds.
+int vla_expert_timeline(vla_handle m, unsigned long long* out, int max_entries, int* n_written) {
+  if (!m || !m->finalized || !out || !n_written) return VLA_ERR_STATE;
+  if (!m->use_xp) return m->fail(VLA_ERR_STATE, "the persistent action-expert kernel is not in use for this handle");
+  cudaSetDevice(m->cfg.device);
+  const int phases = m->nsteps * ((m->pi05 ? 1 : 2) + 6 * m->nl + 1);
+#ifdef XP_FINE_TRACE
+  const int n = std::min(4096, max_entries);   // development build: the in-phase marks sit behind the barrier records
+#else
+  const int n = std::min(std::min(2 * phases, 4096), max_entries);
 #endif
+  CK(cudaMemsetAsync(m->xp_trace, 0, 4096 * sizeof(unsigned long long), m->own_stream));
+  CK(launch_expert_persistent(m, m->own_stream, m->xp_trace));
+  CK(cudaStreamSynchronize(m->own_stream));
+  CK(cudaMemcpy(out, m->xp_trace, (size_t)n * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+  *n_written = n;
+  return VLA_OK;
+}
 
 int vla_op_attention_tc(const vla_attn_tc_desc* d, void* stream) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
