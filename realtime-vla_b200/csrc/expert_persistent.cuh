@@ -3,48 +3,61 @@
 //
 // Decomposition (reference loop: pi0_infer.py:1165-1230, pi05_infer.py:418-523):
 //   * every GEMM is partitioned over OUTPUT FEATURES with the full K per CTA (8-feature tiles, the n8 of
-//     mma.sync.m16n8k16): no split-K exchange, no cluster.  The 51 suffix tokens are the M dimension (4 m16 tiles).
+//     mma.sync.m16n8k16): no split-K exchange, no cluster.  The <= 56 suffix tokens are the M dimension (m16 tiles).
 //   * each CTA's weights are pre-packed at load time into ONE contiguous stream of 16 KB chunks (8 features x 1024 K in
 //     mma B-fragment order) in exactly the order the CTA consumes them; warp 8 copies the stream into a ring of shared
 //     memory slots with cp.async.bulk, decoupled from the phase structure: while the CTA waits at a grid barrier the
 //     weights of the next operators keep arriving from HBM.
-//   * activations are small (<= 51 x 4096 bf16) and live in L2; a phase reads them with cp.async.cg into swizzled
-//     shared memory and feeds the tensor cores with ldmatrix.
+//   * activations are small (<= 56 x 4096 bf16) and live in L2; warp 9 brings them in with TMA (cp.async.bulk.tensor,
+//     128-byte swizzle, 64-wide K blocks) through a ring of four 256-wide K stages as soon as the grid barrier before
+//     the phase is passed; the MMA warps read them with ldmatrix.
 //   * phases are separated by grid barriers (one global counter, red.release / ld.acquire, ~1.1 us for 148 CTAs);
 //     every spin is bounded by %globaltimer and raises the status word instead of hanging.
 //   * the fp32 residual stream is owned by feature: CTA c < 128 keeps x[:, 8c..8c+7] in its shared memory for the whole
 //     kernel; what other CTAs read is the bf16 mirror (GEMM operand) and per-CTA partial sums of squares (the RMS
 //     norms are folded into the consuming GEMMs: norm(x) @ W = f * (x @ W), pi0_infer.py:1005; Pi05 adaRMS as
 //     f * ((x * (1 + scale)) @ W) + shift @ W, pi05_infer.py:78-113).
-//   * suffix attention (408 query rows x <= 1024 keys, head dim 256): 32-row blocks x key splits over the CTAs,
+//   * suffix attention (<= 448 query rows x <= 1024 keys, head dim 256): 32-row blocks x key splits over the CTAs,
 //     single-pass softmax per split, partial outputs merged in a second short phase.
 #pragma once
 #include "common.cuh"
 
 namespace xp {
 
-constexpr int THREADS = 288;          // 8 MMA warps + 1 weight-stream warp
+constexpr int THREADS = 320;          // 8 MMA warps + weight-stream warp + activation (TMA) warp
 constexpr int CTHREADS = 256;
 constexpr int CHUNK_BYTES = 16384;    // 8 features x 1024 K, bf16, fragment order
 constexpr int NSLOT = 6;
-constexpr int MAX_ROWS = 52;          // suffix tokens held in shared memory
-constexpr int A_BYTES = MAX_ROWS * 2048;          // resident A [rows][1024] / 4 streamed stages / K+V of attention
-constexpr int STAGE_BYTES = MAX_ROWS * 512;       // streamed A stage: [rows][256 K]
-constexpr int SCR_BYTES = 16384;                  // GEMM: K-half exchange (8 KB); attention: Q tile (16 KB)
+constexpr int MAX_ROWS = 56;          // suffix tokens held in shared memory
+constexpr int TILE_BYTES = MAX_ROWS * 128;        // one 64-wide K block of the activation rows (TMA box, 128B swizzle)
+constexpr int STAGE_BYTES = 4 * TILE_BYTES;       // 256 K
+constexpr int N_ASTAGE = 4;
+constexpr int A_BYTES = N_ASTAGE * STAGE_BYTES;   // 114688: activation stages / K, V and Q tiles of the attention
+constexpr int SCR_BYTES = 8192;                   // GEMM: K-half exchange; attention: probabilities and row statistics
 constexpr int RING_OFF = A_BYTES + SCR_BYTES;
 constexpr int PERSIST_OFF = RING_OFF + NSLOT * CHUNK_BYTES;
-constexpr int PERSIST_BYTES = 4096;
-constexpr int SMEM_BYTES = PERSIST_OFF + PERSIST_BYTES + 128;
+constexpr int PERSIST_BYTES = 10240;          // barriers, per-token scales, this CTA's stream slice, rotary table of its QKV tiles
+constexpr int SMEM_BYTES = PERSIST_OFF + PERSIST_BYTES + 1024;   // + slack to align the base to 1024 B
+constexpr float SSQ_FIX = 16777216.0f;   // sums of squares travel as 40.24 fixed point: integer adds are order independent
 constexpr int N_OWNERS = 128;         // CTAs that own 8 features of the 1024-wide stream / 32 hidden features
 constexpr int CH_PER_LAYER = 17;      // stream slots per layer: qkv 0-2, o 3-4, (gate,up) x4 5-12, down 13-16
 constexpr int ATT_ROWS = 32;          // query rows per attention work item
 constexpr int ATT_MAX_KEYS = 96;      // keys per split
+constexpr int ATT_V_OFF = ATT_MAX_KEYS * 512;     // V tiles behind the K tiles
+constexpr int ATT_Q_OFF = 2 * ATT_MAX_KEYS * 512; // Q tiles (16 KB) fill the rest of the activation region
 
 struct Params {
+  CUtensorMap tm_xb;      // bf16 mirror of the stream [S, 1024], box 64 x S
+  CUtensorMap tm_act;     // Pi0 action MLP input [C, 1024], box 64 x C
+  CUtensorMap tm_attn;    // attention output [S, 2048], box 64 x S
+  CUtensorMap tm_hidden;  // MLP hidden [S, 4096], box 64 x S
+  CUtensorMap tm_q;       // queries as [S * 8, 256], box 64 x 32
+  CUtensorMap tm_k;       // key cache [layers * T, 256], box 64 x att_kps
+  CUtensorMap tm_v;       // value cache, same
   int pi05, S, C, P, T, nl, nsteps, G;
   int att_nrb, att_ks, att_kps;   // row blocks, key splits, keys per split (multiple of 16, <= ATT_MAX_KEYS)
   const uint4* wstream;           // [G][chunks_per_cta][1024] uint4
-  int chunks_per_cta;             // nl_alloc * CH_PER_LAYER + 2   (misc: +0 action MLP (Pi0), +1 out projection)
+  int chunks_per_cta;             // layers * CH_PER_LAYER + 2   (misc: +0 action MLP (Pi0), +1 out projection)
   int misc_base;
   const bf16* w_in;               // action in-projection, K-major [1024][64]
   const float* b_in;              // Pi0: time biases [steps][ld_b_in]; Pi05: bias [1024]
@@ -57,7 +70,8 @@ struct Params {
   const float* sw_fin;            // Pi05: shift_fin @ W_out per step [steps][32]
   const float *style_attn, *style_ffn, *style_fin;   // Pi05 [step][layer][3072] / [step][3072]
   const float *sw_qkv, *sw_gate, *sw_up;             // Pi05 shift @ W per (step, layer)
-  bf16* noise; float* noise_f32; bf16* act; float* x_out; bf16* xb; float* ssq;
+  bf16* noise; float* noise_f32; bf16* act; float* x_out; bf16* xb;
+  unsigned long long* ssq;        // [3][64] per-token sums of squares of the stream, fixed point, rotating buffers (zeroed with bar_ctr)
   bf16* q; bf16* kcache; bf16* vcache; bf16* attn; bf16* hidden;
   float* att_part; float* att_stat;
   const float *rope_cos, *rope_sin;
@@ -79,9 +93,9 @@ __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uin
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-// 16-byte global -> shared copy through L2 only; src_bytes = 0 zero-fills the destination
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+// 16-byte global -> shared copy through L2 only
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -97,24 +111,31 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
 }
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
-// byte offset of 16-byte chunk `ch` of row `row` in a swizzled tile with `pitch` bytes per row (pitch % 128 == 0)
-__host__ __device__ __forceinline__ uint32_t swz(int row, int ch, int pitch) { return (uint32_t)(row * pitch + ((ch ^ (row & 7)) << 4)); }
+// Byte offset, inside a tile of 128-byte rows written by TMA with the 128-byte swizzle (tile base 1024-aligned), of the
+// 16-byte chunk `ch` (0..7) of row `row`.
+__host__ __device__ __forceinline__ uint32_t swz128(int row, int ch) { return (uint32_t)(row * 128 + ((ch ^ (row & 7)) << 4)); }
 
 // ---- shared state ------------------------------------------------------------------------------------------------------
 struct Ctx {
   const Params* p;
-  uint32_t sbase;         // shared address of the A region
+  uint32_t sbase;         // shared address of the activation region (1024-aligned)
   uint8_t* sptr;          // generic pointer to the same
-  uint32_t full_bar, empty_bar;
+  uint32_t w_full, w_empty, a_full, a_empty, att_full;
+  volatile int* go_count; // grid barriers passed, published by thread 0 for the activation warp
   volatile int* s_abort;
   float* fs;              // [64] per-token RMS scale
   float* xs;              // [64][8] this CTA's slice of the residual stream
   float* sttok;           // [8]
-  unsigned int chunk_g;   // chunks consumed so far (consumer side)
+  float2* rope;           // [3 tiles][4 pairs][64 rows] (cos, sin) of this CTA's QKV features at the suffix positions
+  unsigned int pk;        // residual-stream producer phases completed (selects the sum-of-squares buffer)
+  unsigned int chunk_g;   // weight chunks consumed so far
+  unsigned int a_g;       // activation stages consumed so far
+  unsigned int att_n;     // attention phases run so far
   unsigned int bar_epoch; // grid barriers passed
   int cta, warp, lane, tid;
   int valid_len, pos_base;
@@ -123,10 +144,11 @@ struct Ctx {
 
 // development timeline inside phases: CTA 0, thread 0, Euler step 0, layer 1 only -> trace[2560 + id]
 #ifdef XP_FINE_TRACE
-#define XP_MARK(c, id) do { if ((c).fine && (c).tid == 0) (c).p->trace[2560 + (id)] = globaltimer_ns(); } while (0)
+#define XP_MARK(c, id) do { if ((c).fine && (c).tid == 0) (c).p->trace[2560 + (id)] = (unsigned long long)clock64(); } while (0)
 #else
 #define XP_MARK(c, id) do {} while (0)
 #endif
+
 __device__ __forceinline__ bool poll_abort(Ctx& c) {
   if (*c.s_abort) return true;
   if (*reinterpret_cast<volatile unsigned int*>(c.p->bar_ctr + 1)) { *c.s_abort = 1; return true; }
@@ -152,15 +174,21 @@ __device__ __forceinline__ bool wait_bar(Ctx& c, uint32_t bar, uint32_t parity) 
     }
   }
 }
-// shared address of ring slot holding the g-th chunk, after waiting for it
+// shared address of the ring slot holding the g-th weight chunk, after waiting for it
 __device__ __forceinline__ uint32_t acquire_chunk(Ctx& c, unsigned int g, bool* ok) {
   const unsigned int s = g % NSLOT;
-  if (!wait_bar(c, c.full_bar + 8 * s, (g / NSLOT) & 1u)) *ok = false;
+  if (!wait_bar(c, c.w_full + 8 * s, (g / NSLOT) & 1u)) *ok = false;
   return c.sbase + RING_OFF + s * CHUNK_BYTES;
 }
 __device__ __forceinline__ void release_chunk(Ctx& c, unsigned int g) {
   __syncwarp();
-  if (c.lane == 0) mbar_arrive(c.empty_bar + 8 * (g % NSLOT));
+  if (c.lane == 0) mbar_arrive(c.w_empty + 8 * (g % NSLOT));
+}
+// activation stage g of the ring (256 K of all rows): wait / hand back
+__device__ __forceinline__ bool a_wait(Ctx& c, unsigned int g) { return wait_bar(c, c.a_full + 8 * (g & 3u), (g >> 2) & 1u); }
+__device__ __forceinline__ void a_release(Ctx& c, unsigned int g) {
+  __syncwarp();
+  if (c.lane == 0) mbar_arrive(c.a_empty + 8 * (g & 3u));
 }
 
 // Grid-wide barrier of the MMA warps of all CTAs.  Returns false after a timeout / abort.
@@ -187,6 +215,7 @@ __device__ __forceinline__ bool grid_barrier(Ctx& c, int trace_slot) {
       }
     }
     __threadfence();
+    *c.go_count = (int)c.bar_epoch;    // the activation warp may now fetch what the other CTAs wrote
     if (p.trace && c.cta == 0) p.trace[2 * trace_slot + 1] = globaltimer_ns();
   } else {
     ++c.bar_epoch;
@@ -195,133 +224,140 @@ __device__ __forceinline__ bool grid_barrier(Ctx& c, int trace_slot) {
   return *c.s_abort == 0;
 }
 
-// ---- A operand loaders ---------------------------------------------------------------------------------------------------
-// resident: rows x K bf16 (K <= 1024, K % 8 == 0) from global (row pitch ld elements) into the swizzled [rows][2048 B] tile
-__device__ __forceinline__ void load_a_resident(Ctx& c, const bf16* src, int rows, int K, int ld) {
-  const int cpr = K >> 3;
-  for (int idx = c.tid; idx < rows * cpr; idx += CTHREADS) {
-    const int row = idx / cpr, ch = idx - row * cpr;
-    cp_async16(c.sbase + swz(row, ch, 2048), src + (size_t)row * ld + ch * 8, 16);
-  }
-  cp_async_commit();
+// Per-token RMS scale: the owners of the stream add their partial sums of squares (fixed point) into one word per token
+// with integer atomics, so the sum does not depend on the order; fs[t] = rsqrt(ssq[t] / 1024 + 1e-6).
+// The load is issued at the start of a phase and consumed after its MMAs.
+__device__ __forceinline__ unsigned long long fs_issue(const Ctx& c) {
+  return c.tid < 64 ? __ldcg(c.p->ssq + ((c.pk + 2u) % 3u) * 64 + c.tid) : 0ull;   // buffer of producer phase pk - 1
 }
-// per-token RMS scale from the producers' partial sums of squares: fs[t] = rsqrt(sum_slots ssq[slot][t] / 1024 + 1e-6)
-__device__ __forceinline__ void compute_fs(Ctx& c) {
-  const int t = c.tid >> 2, part = c.tid & 3;
-  float acc = 0.f;
-  for (int s = part * 32; s < part * 32 + 32; ++s) acc += __ldcg(c.p->ssq + s * 64 + t);
-  acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-  acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-  if (part == 0) c.fs[t] = rsqrtf(acc * (1.0f / 1024.0f) + 1e-6f);
+__device__ __forceinline__ void fs_finish(Ctx& c, unsigned long long v) {
+  if (c.tid < 64) c.fs[c.tid] = rsqrtf((float)v * (1.0f / (SSQ_FIX * 1024.0f)) + 1e-6f);
+}
+// producer side: called once per producer phase by every MMA thread of every CTA
+__device__ __forceinline__ void ssq_rotate(Ctx& c) {
+  if (c.cta == 0 && c.tid < 64) c.p->ssq[((c.pk + 1u) % 3u) * 64 + c.tid] = 0ull;   // next phase's buffer, idle since two phases
+}
+__device__ __forceinline__ void ssq_add(const Ctx& c, int token, float sq) {
+  atomicAdd(c.p->ssq + (c.pk % 3u) * 64 + token, (unsigned long long)__float2ull_rn(sq * SSQ_FIX));
 }
 
 // ---- GEMM cores ------------------------------------------------------------------------------------------------------------
-// NT feature tiles (their chunks at slot addresses sl[0..NT-1]) against the resident A tile; this warp's K half.
+// NT feature tiles (their chunks at slot addresses sl[0..NT-1]) against the four activation stages a_g0..a_g0+3 (K = 1024);
+// warp (mi, kh) takes rows 16 mi.. and K half kh.  The loop is bound by shared-memory bandwidth (1 KB of A and NT x 512 B
+// of B per iteration and warp), so the more tiles share an A fragment the better.
 template <int NT>
-__device__ __forceinline__ void mma_resident(const Ctx& c, const uint32_t* sl, int rows, int k_steps_pairs, float (&acc)[NT][4]) {
+__device__ __forceinline__ void mma_resident(Ctx& c, const uint32_t* sl, int rows, unsigned int a_g0, float (&acc)[NT][4], bool* ok) {
   const int mi = c.warp & 3, kh = c.warp >> 2;
-  float acc2[NT][4];
+  float acc2[4] = {0.f, 0.f, 0.f, 0.f};   // a single tile alternates two accumulators to break the dependent chain
 #pragma unroll
   for (int t = 0; t < NT; ++t)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) { acc[t][j] = 0.f; acc2[t][j] = 0.f; }
-  if (16 * mi >= rows) return;
+    for (int j = 0; j < 4; ++j) acc[t][j] = 0.f;
+  // every warp waits for the stages of its K half, also a warp without rows: the stages are then handed back in step
+  if (!a_wait(c, a_g0 + 2 * kh) || !a_wait(c, a_g0 + 2 * kh + 1)) *ok = false;
+  if (16 * mi >= rows || !*ok) return;
   const int row = min(16 * mi + (c.lane & 15), rows - 1);
-  const uint32_t a_row = c.sbase + row * 2048;
-  const int rx = row & 7, hi = c.lane >> 4;
-  const int half = k_steps_pairs >> 1;
-  const int sp0 = kh * half, sp1 = sp0 + half;
-#pragma unroll 4
-  for (int sp = sp0; sp < sp1; ++sp) {
-    uint4 b[NT];
-#pragma unroll
-    for (int t = 0; t < NT; ++t) b[t] = lds128(sl[t] + (uint32_t)(sp * 32 + c.lane) * 16);
-    uint32_t a0, a1, a2, a3, e0, e1, e2, e3;
-    const int kc = 4 * sp + hi;
-    ldsm_x4(a_row + (uint32_t)(((kc) ^ rx) << 4), a0, a1, a2, a3);
-    ldsm_x4(a_row + (uint32_t)(((kc + 2) ^ rx) << 4), e0, e1, e2, e3);
+  const int hi = c.lane >> 4;
+  const uint32_t lane_off = (uint32_t)c.lane * 16;
+  const uint32_t a_off0 = swz128(row, hi), a_off1 = swz128(row, hi + 2), a_off2 = swz128(row, hi + 4), a_off3 = swz128(row, hi + 6);
+#pragma unroll 2
+  for (int i = 0; i < 8; ++i) {          // one 64-wide K block (four k16 steps) per round
+    const int kb = 8 * kh + i;
+    const uint32_t tile = c.sbase + (uint32_t)((a_g0 + (kb >> 2)) & 3u) * STAGE_BYTES + (uint32_t)(kb & 3) * TILE_BYTES;
+    uint32_t a[16];
+    ldsm_x4(tile + a_off0, a[0], a[1], a[2], a[3]);
+    ldsm_x4(tile + a_off1, a[4], a[5], a[6], a[7]);
+    ldsm_x4(tile + a_off2, a[8], a[9], a[10], a[11]);
+    ldsm_x4(tile + a_off3, a[12], a[13], a[14], a[15]);
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
-      mma16816(acc[t], a0, a1, a2, a3, b[t].x, b[t].y);
-      mma16816(acc2[t], e0, e1, e2, e3, b[t].z, b[t].w);
+      const uint4 b0 = lds128(sl[t] + (uint32_t)(2 * kb) * 512 + lane_off);
+      const uint4 b1 = lds128(sl[t] + (uint32_t)(2 * kb + 1) * 512 + lane_off);
+      float* second = NT == 1 ? acc2 : acc[t];
+      mma16816(acc[t], a[0], a[1], a[2], a[3], b0.x, b0.y);
+      mma16816(second, a[4], a[5], a[6], a[7], b0.z, b0.w);
+      mma16816(acc[t], a[8], a[9], a[10], a[11], b1.x, b1.y);
+      mma16816(second, a[12], a[13], a[14], a[15], b1.z, b1.w);
     }
   }
+  if (NT == 1) {
 #pragma unroll
-  for (int t = 0; t < NT; ++t)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) acc[t][j] += acc2[t][j];
+    for (int j = 0; j < 4; ++j) acc[0][j] += acc2[j];
+  }
+}
+// every warp hands the four stages of a K = 1024 phase back
+__device__ __forceinline__ void a_release4(Ctx& c) {
+  __syncwarp();
+  if (c.lane == 0)
+    for (int s = 0; s < 4; ++s) mbar_arrive(c.a_empty + 8 * ((c.a_g + s) & 3u));
+  c.a_g += 4;
 }
 
-// Adds the partial accumulators of the K-half-1 warps to those of the K-half-0 warps through shared memory.  After the
-// call the warps with kh == 0 hold the sums.  `buf` alternates between consecutive calls (see the WAR note in the text).
+// Adds the partial accumulators of the K-half-1 warps to those of the K-half-0 warps through shared memory (8 KB:
+// [mi (4)][tile (4)][lane (32)] float4).  After the call the warps with kh == 0 hold the sums.  A second call within
+// one phase passes pre_sync: the extra barrier keeps its writes behind the reads of the first call.
 template <int NT>
-__device__ __forceinline__ void reduce_khalves(const Ctx& c, int buf, float (&acc)[NT][4]) {
+__device__ __forceinline__ void reduce_khalves(const Ctx& c, bool pre_sync, float (&acc)[NT][4]) {
+  static_assert(NT <= 4, "the exchange area holds four tiles per warp");
   const int mi = c.warp & 3, kh = c.warp >> 2;
-  float4* red = reinterpret_cast<float4*>(c.sptr + A_BYTES) + (size_t)buf * 256;   // [buf][mi][t(2)][lane]
+  float4* red = reinterpret_cast<float4*>(c.sptr + A_BYTES) + mi * 128 + c.lane;
+  if (pre_sync) cbar();
   if (kh == 1) {
 #pragma unroll
-    for (int t = 0; t < NT; ++t) red[(mi * 2 + t) * 32 + c.lane] = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
+    for (int t = 0; t < NT; ++t) red[t * 32] = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
   }
   cbar();
   if (kh == 0) {
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
-      const float4 v = red[(mi * 2 + t) * 32 + c.lane];
+      const float4 v = red[t * 32];
       acc[t][0] += v.x; acc[t][1] += v.y; acc[t][2] += v.z; acc[t][3] += v.w;
     }
   }
 }
 
-// One feature tile (chunks g0 .. g0 + K/1024 - 1) against A rows streamed from global [rows][K] in 256-wide K stages.
-__device__ __forceinline__ bool mma_streamed(Ctx& c, const bf16* src, int rows, int K, float (&acc)[1][4]) {
+// One feature tile (weight chunks chunk_g .. chunk_g + K/1024 - 1) against K/256 activation stages streamed through the ring.
+__device__ __forceinline__ bool mma_streamed(Ctx& c, int rows, int K, float (&acc)[1][4]) {
   const int mi = c.warp & 3, kh = c.warp >> 2;
   const int n_stages = K >> 8;
   bool ok = true;
   float acc2[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int j = 0; j < 4; ++j) acc[0][j] = 0.f;
-  auto load_stage = [&](int st) {
-    const uint32_t base = c.sbase + (uint32_t)(st & 3) * STAGE_BYTES;
-    const bf16* s0 = src + (size_t)st * 256;
-    for (int idx = c.tid; idx < rows * 32; idx += CTHREADS) {
-      const int row = idx >> 5, ch = idx & 31;
-      cp_async16(base + swz(row, ch, 512), s0 + (size_t)row * K + ch * 8, 16);
-    }
-  };
-  XP_MARK(c, K == 2048 ? 20 : 40);
-  for (int st = 0; st < 3; ++st) {
-    if (st < n_stages) load_stage(st);
-    cp_async_commit();
-  }
-  XP_MARK(c, K == 2048 ? 21 : 41);
   const bool active = 16 * mi < rows;
   const int row = min(16 * mi + (c.lane & 15), rows - 1);
-  const int rx = row & 7, hi = c.lane >> 4;
+  const int hi = c.lane >> 4;
   uint32_t slot = 0;
   for (int st = 0; st < n_stages; ++st) {
-    cp_async_wait<2>();
-    cbar();
-    if (st + 3 < n_stages) load_stage(st + 3);
-    cp_async_commit();
+    const unsigned int g = c.a_g + st;
     if ((st & 3) == 0) slot = acquire_chunk(c, c.chunk_g + (st >> 2), &ok);
-    if (active && ok) {
-      const uint32_t a_row = c.sbase + (uint32_t)(st & 3) * STAGE_BYTES + row * 512;
+    if (!a_wait(c, g)) ok = false;   // also a warp without rows: keeps the hand-back of the stages in step
+    if (active) {
+      if (ok) {
+        const uint32_t stage = c.sbase + (uint32_t)(g & 3u) * STAGE_BYTES;
+        const uint32_t bsrc = slot + (uint32_t)(((st & 3) * 8 + 4 * kh) * 32 + c.lane) * 16;
+        uint4 b[4];
+        uint32_t a[4][8];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int spl = 4 * kh + i;
-        const uint4 b = lds128(slot + (uint32_t)((((st & 3) * 8 + spl) * 32) + c.lane) * 16);
-        uint32_t a0, a1, a2, a3, e0, e1, e2, e3;
-        const int kc = 4 * spl + hi;
-        ldsm_x4(a_row + (uint32_t)((kc ^ rx) << 4), a0, a1, a2, a3);
-        ldsm_x4(a_row + (uint32_t)(((kc + 2) ^ rx) << 4), e0, e1, e2, e3);
-        mma16816(acc[0], a0, a1, a2, a3, b.x, b.y);
-        mma16816(acc2, e0, e1, e2, e3, b.z, b.w);
+        for (int i = 0; i < 4; ++i) {      // all fragment loads of the stage first, then its eight MMAs
+          const int spl = 4 * kh + i;
+          b[i] = lds128(bsrc + i * 512);
+          const uint32_t tile = stage + (uint32_t)(spl >> 1) * TILE_BYTES;
+          const int c0 = 4 * (spl & 1) + hi;
+          ldsm_x4(tile + swz128(row, c0), a[i][0], a[i][1], a[i][2], a[i][3]);
+          ldsm_x4(tile + swz128(row, c0 + 2), a[i][4], a[i][5], a[i][6], a[i][7]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          mma16816(acc[0], a[i][0], a[i][1], a[i][2], a[i][3], b[i].x, b[i].y);
+          mma16816(acc2, a[i][4], a[i][5], a[i][6], a[i][7], b[i].z, b[i].w);
+        }
       }
     }
+    a_release(c, g);
     if ((st & 3) == 3) release_chunk(c, c.chunk_g + (st >> 2));
-    XP_MARK(c, (K == 2048 ? 22 : 42) + st);
   }
-  cp_async_wait<0>();
+  c.a_g += (unsigned int)n_stages;
   c.chunk_g += (unsigned int)(K >> 10);
 #pragma unroll
   for (int j = 0; j < 4; ++j) acc[0][j] += acc2[j];
@@ -333,18 +369,23 @@ struct ResidEpi {
   int rows;          // valid A rows
   int row_off;       // output token = A row + row_off
   bool accumulate;   // x += gate * acc (else x = acc + bias)
-  const float* bias; // [1024] or null
-  const float* gate; // [1024] or null (1)
-  const float* mscale;  // [1024] or null: mirror = x * (1 + mscale[n])
+  float b0, b1, g0, g1, m0, m1;   // bias, gate and mirror scale (1 + adaRMS scale of the consuming norm) of features n, n+1
 };
+__device__ __forceinline__ ResidEpi make_resid(Ctx& c, int rows, int row_off, bool accumulate, const float* bias, const float* gate,
+                                               const float* mscale) {
+  const int n = 8 * c.cta + 2 * (c.lane & 3);
+  ResidEpi e;
+  e.rows = rows; e.row_off = row_off; e.accumulate = accumulate;
+  e.b0 = bias ? bias[n] : 0.f; e.b1 = bias ? bias[n + 1] : 0.f;
+  e.g0 = gate ? gate[n] : 1.f; e.g1 = gate ? gate[n + 1] : 1.f;
+  e.m0 = mscale ? 1.f + mscale[n] : 1.f; e.m1 = mscale ? 1.f + mscale[n + 1] : 1.f;
+  return e;
+}
 // residual-stream update for this CTA's 8 features; writes the bf16 mirror, the fp32 copy and the partial sums of squares
 __device__ __forceinline__ void epi_resid(Ctx& c, const ResidEpi& e, const float* acc) {
   const Params& p = *c.p;
   const int mi = c.warp & 3;
   const int j0 = 2 * (c.lane & 3), n = 8 * c.cta + j0;
-  const float b0 = e.bias ? e.bias[n] : 0.f, b1 = e.bias ? e.bias[n + 1] : 0.f;
-  const float g0 = e.gate ? e.gate[n] : 1.f, g1 = e.gate ? e.gate[n + 1] : 1.f;
-  const float m0 = e.mscale ? 1.f + e.mscale[n] : 1.f, m1 = e.mscale ? 1.f + e.mscale[n + 1] : 1.f;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = 16 * mi + (c.lane >> 2) + 8 * h;
@@ -353,54 +394,70 @@ __device__ __forceinline__ void epi_resid(Ctx& c, const ResidEpi& e, const float
     float v0 = 0.f, v1 = 0.f;
     if (valid) {
       if (e.accumulate) {
-        v0 = c.xs[t * 8 + j0] + g0 * acc[2 * h];
-        v1 = c.xs[t * 8 + j0 + 1] + g1 * acc[2 * h + 1];
+        v0 = c.xs[t * 8 + j0] + e.g0 * acc[2 * h];
+        v1 = c.xs[t * 8 + j0 + 1] + e.g1 * acc[2 * h + 1];
       } else {
-        v0 = acc[2 * h] + b0;
-        v1 = acc[2 * h + 1] + b1;
+        v0 = acc[2 * h] + e.b0;
+        v1 = acc[2 * h + 1] + e.b1;
       }
       c.xs[t * 8 + j0] = v0;
       c.xs[t * 8 + j0 + 1] = v1;
-      *reinterpret_cast<uint32_t*>(p.xb + (size_t)t * 1024 + n) = pack_bf16x2(v0 * m0, v1 * m1);
+      *reinterpret_cast<uint32_t*>(p.xb + (size_t)t * 1024 + n) = pack_bf16x2(v0 * e.m0, v1 * e.m1);
       *reinterpret_cast<float2*>(p.x_out + (size_t)t * 1024 + n) = make_float2(v0, v1);
     }
     float sq = v0 * v0 + v1 * v1;
     sq += __shfl_xor_sync(0xffffffffu, sq, 1);
     sq += __shfl_xor_sync(0xffffffffu, sq, 2);
-    if (valid && (c.lane & 3) == 0) p.ssq[c.cta * 64 + t] = sq;
+    if (valid && (c.lane & 3) == 0) ssq_add(c, t, sq);
   }
 }
 
 // ---- phases ----------------------------------------------------------------------------------------------------------------
 // Action in-projection (K = 32) straight from global weights: Pi0 -> act = silu(noise @ W + time_bias[step]);
-// Pi05 -> x = noise @ W + b (start of the residual stream).  CTA c < 128 owns features 8c..8c+7.
+// Pi05 -> x = noise @ W + b (start of the residual stream).  CTA c < 128 owns features 8c..8c+7.  The 50 x 32 noise
+// tile is brought in by the MMA threads themselves (the activation ring is idle between phases).
 __device__ __forceinline__ void phase_in_proj(Ctx& c, int step) {
   const Params& p = *c.p;
-  if (c.cta >= N_OWNERS) return;
-  load_a_resident(c, p.noise, p.C, 32, 32);
+  if (p.pi05) ssq_rotate(c);
+  if (c.cta >= N_OWNERS) { if (p.pi05) ++c.pk; return; }
+  for (int idx = c.tid; idx < p.C * 4; idx += CTHREADS) {
+    const int row = idx >> 2, ch = idx & 3;
+    cp_async16(c.sbase + swz128(row, ch), p.noise + (size_t)row * 32 + ch * 8);
+  }
+  cp_async_commit();
+  const int mi = c.warp & 3, kh = c.warp >> 2;
+  const int j0 = 2 * (c.lane & 3), n = 8 * c.cta + j0;
+  float b0 = 0.f, b1 = 0.f;
+  ResidEpi e;
+  if (!p.pi05) {
+    const float* tb = p.b_in + (size_t)step * p.ld_b_in;
+    b0 = tb[n]; b1 = tb[n + 1];
+  } else {
+    e = make_resid(c, p.C, 0, false, p.b_in, nullptr, p.style_attn + (size_t)step * p.nl * 3072);   // pre-attention norm of layer 0
+  }
+  const int nb = 8 * c.cta + (c.lane >> 2);
+  uint32_t wb[2][2];
+#pragma unroll
+  for (int s = 0; s < 2; ++s) {
+    const bf16* w = p.w_in + (size_t)nb * 64 + 16 * s + 2 * (c.lane & 3);
+    wb[s][0] = *reinterpret_cast<const uint32_t*>(w);
+    wb[s][1] = *reinterpret_cast<const uint32_t*>(w + 8);
+  }
   cp_async_wait<0>();
   cbar();
-  const int mi = c.warp & 3, kh = c.warp >> 2;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   if (kh == 0 && 16 * mi < p.C) {
     const int row = min(16 * mi + (c.lane & 15), p.C - 1);
-    const uint32_t a_row = c.sbase + row * 2048;
-    const int rx = row & 7, hi = c.lane >> 4;
-    const int nb = 8 * c.cta + (c.lane >> 2);
+    const int hi = c.lane >> 4;
 #pragma unroll
     for (int s = 0; s < 2; ++s) {
       uint32_t a0, a1, a2, a3;
-      ldsm_x4(a_row + (uint32_t)(((2 * s + hi) ^ rx) << 4), a0, a1, a2, a3);
-      const bf16* w = p.w_in + (size_t)nb * 64 + 16 * s + 2 * (c.lane & 3);
-      const uint32_t b0 = *reinterpret_cast<const uint32_t*>(w), b1 = *reinterpret_cast<const uint32_t*>(w + 8);
-      mma16816(acc, a0, a1, a2, a3, b0, b1);
+      ldsm_x4(c.sbase + swz128(row, 2 * s + hi), a0, a1, a2, a3);
+      mma16816(acc, a0, a1, a2, a3, wb[s][0], wb[s][1]);
     }
   }
   if (kh == 0) {
     if (!p.pi05) {
-      const int j0 = 2 * (c.lane & 3), n = 8 * c.cta + j0;
-      const float* tb = p.b_in + (size_t)step * p.ld_b_in;
-      const float b0 = tb[n], b1 = tb[n + 1];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int r = 16 * mi + (c.lane >> 2) + 8 * h;
@@ -408,33 +465,27 @@ __device__ __forceinline__ void phase_in_proj(Ctx& c, int step) {
           *reinterpret_cast<uint32_t*>(p.act + (size_t)r * 1024 + n) = pack_bf16x2(silu_f(acc[2 * h] + b0), silu_f(acc[2 * h + 1] + b1));
       }
     } else {
-      ResidEpi e;
-      e.rows = p.C; e.row_off = 0; e.accumulate = false; e.bias = p.b_in; e.gate = nullptr;
-      e.mscale = p.style_attn + (size_t)step * p.nl * 3072;   // pre-attention norm of layer 0
       epi_resid(c, e, acc);
     }
   }
+  if (p.pi05) ++c.pk;
 }
 
 // Pi0 action MLP: x[1 + a] = act[a] @ W + b; x[0] = state token.
 __device__ __forceinline__ bool phase_action_mlp(Ctx& c) {
   const Params& p = *c.p;
-  if (c.cta >= N_OWNERS) return true;
+  ssq_rotate(c);
+  if (c.cta >= N_OWNERS) { ++c.pk; return true; }
   bool ok = true;
-  load_a_resident(c, p.act, p.C, 1024, 1024);
+  const ResidEpi e = make_resid(c, p.C, 1, false, p.b_mlp, nullptr, nullptr);
   const uint32_t sl = acquire_chunk(c, c.chunk_g, &ok);
-  cp_async_wait<0>();
-  cbar();
   float acc[1][4];
-  if (ok) mma_resident<1>(c, &sl, p.C, 32, acc);
+  mma_resident<1>(c, &sl, p.C, c.a_g, acc, &ok);
   release_chunk(c, c.chunk_g);
+  a_release4(c);
   c.chunk_g += 1;
-  reduce_khalves<1>(c, 0, acc);
-  if ((c.warp >> 2) == 0) {
-    ResidEpi e;
-    e.rows = p.C; e.row_off = 1; e.accumulate = false; e.bias = p.b_mlp; e.gate = nullptr; e.mscale = nullptr;
-    epi_resid(c, e, acc[0]);
-  }
+  reduce_khalves<1>(c, false, acc);
+  if ((c.warp >> 2) == 0) epi_resid(c, e, acc[0]);
   if (c.tid < 8) {   // the state token row (constant over the Euler steps)
     const float v = c.sttok[c.tid];
     c.xs[c.tid] = v;
@@ -444,81 +495,80 @@ __device__ __forceinline__ bool phase_action_mlp(Ctx& c) {
     sq += __shfl_xor_sync(0xffu, sq, 1);
     sq += __shfl_xor_sync(0xffu, sq, 2);
     sq += __shfl_xor_sync(0xffu, sq, 4);
-    if (c.tid == 0) p.ssq[c.cta * 64] = sq;
+    if (c.tid == 0) ssq_add(c, 0, sq);
   }
+  ++c.pk;
   return ok;
 }
 
 // QKV projection with folded norm, rotary embedding and K/V-cache append (pi0_infer.py:777-810).
 // CTA c owns feature tiles c, c + G, c + 2G (< 320).
-__device__ __forceinline__ bool phase_qkv(Ctx& c, int step, int layer) {
+template <int NQ>
+__device__ __forceinline__ bool qkv_tiles(Ctx& c, int step, int layer) {
   const Params& p = *c.p;
   bool ok = true;
-  const int nq = (c.cta + 2 * p.G < 320) ? 3 : ((c.cta + p.G < 320) ? 2 : (c.cta < 320 ? 1 : 0));
-  if (nq == 0) return true;
-  XP_MARK(c, 0);
-  load_a_resident(c, p.xb, p.S, 1024, 1024);
-  XP_MARK(c, 1);
-  compute_fs(c);
-  XP_MARK(c, 2);
-  uint32_t sl[3];
-  for (int j = 0; j < nq; ++j) sl[j] = acquire_chunk(c, c.chunk_g + j, &ok);
-  XP_MARK(c, 3);
-  cp_async_wait<0>();
-  XP_MARK(c, 4);
-  cbar();
-  XP_MARK(c, 5);
   const int mi = c.warp & 3, kh = c.warp >> 2;
-  const float* bias = p.pi05 ? p.sw_qkv + ((size_t)step * p.nl + layer) * 2560 : nullptr;
-  bf16* kc = p.kcache + (size_t)layer * p.T * 256;
-  bf16* vc = p.vcache + (size_t)layer * p.T * 256;
-  auto epilogue = [&](int tile, const float* acc) {
-    const int n = 8 * tile + 2 * (c.lane & 3);
-    const float b0 = bias ? bias[n] : 0.f, b1 = bias ? bias[n + 1] : 0.f;
-    const bool rot = n < 2304;
-    const int fi = (n & 255) >> 1;
+  // the few values the epilogue needs from global memory are requested before the MMAs
+  float bias[NQ][2];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int r = 16 * mi + (c.lane >> 2) + 8 * h;
-      if (r >= p.S) continue;
-      const float f = c.fs[r];
-      float v0 = f * acc[2 * h] + b0, v1 = f * acc[2 * h + 1] + b1;
-      if (rot) {
-        const int pos = c.pos_base + r;
-        const float cs = p.rope_cos[pos * 128 + fi], sn = p.rope_sin[pos * 128 + fi];
-        const float y0 = v0 * cs - v1 * sn, y1 = v1 * cs + v0 * sn;
-        v0 = y0; v1 = y1;
-      }
-      const uint32_t o = pack_bf16x2(v0, v1);
-      if (n < 2048) *reinterpret_cast<uint32_t*>(p.q + (size_t)r * 2048 + n) = o;
-      else if (n < 2304) *reinterpret_cast<uint32_t*>(kc + (size_t)(p.P + r) * 256 + (n - 2048)) = o;
-      else *reinterpret_cast<uint32_t*>(vc + (size_t)(p.P + r) * 256 + (n - 2304)) = o;
-    }
-  };
-  {
-    float acc[2][4];
-    if (nq >= 2) {
-      if (ok) mma_resident<2>(c, sl, p.S, 32, acc);
-      XP_MARK(c, 6);
-      release_chunk(c, c.chunk_g);
-      release_chunk(c, c.chunk_g + 1);
-      reduce_khalves<2>(c, 0, acc);
-      XP_MARK(c, 7);
-      if (kh == 0) { epilogue(c.cta, acc[0]); epilogue(c.cta + p.G, acc[1]); }
-      XP_MARK(c, 8);
-    }
-    if (nq == 1 || nq == 3) {
-      float a1[1][4];
-      const uint32_t s1 = sl[nq - 1];
-      if (ok) mma_resident<1>(c, &s1, p.S, 32, a1);
-      release_chunk(c, c.chunk_g + nq - 1);
-      reduce_khalves<1>(c, 1, a1);
-      if (kh == 0) epilogue(c.cta + (nq - 1) * p.G, a1[0]);
-      XP_MARK(c, 9);
+  for (int t = 0; t < NQ; ++t) { bias[t][0] = 0.f; bias[t][1] = 0.f; }
+  if (p.pi05 && kh == 0) {
+    const float* bsrc = p.sw_qkv + ((size_t)step * p.nl + layer) * 2560;
+#pragma unroll
+    for (int t = 0; t < NQ; ++t) {
+      const int n = 8 * (c.cta + t * p.G) + 2 * (c.lane & 3);
+      bias[t][0] = bsrc[n];
+      bias[t][1] = bsrc[n + 1];
     }
   }
-  c.chunk_g += (unsigned int)nq;
+  const unsigned long long fv = fs_issue(c);
+  uint32_t sl[NQ];
+#pragma unroll
+  for (int j = 0; j < NQ; ++j) sl[j] = acquire_chunk(c, c.chunk_g + j, &ok);
+  XP_MARK(c, 1);
+  float acc[NQ][4];
+  mma_resident<NQ>(c, sl, p.S, c.a_g, acc, &ok);
+  XP_MARK(c, 2);
+#pragma unroll
+  for (int j = 0; j < NQ; ++j) release_chunk(c, c.chunk_g + j);
+  a_release4(c);
+  c.chunk_g += NQ;
+  fs_finish(c, fv);
+  reduce_khalves<NQ>(c, false, acc);   // the barrier inside also publishes fs
+  XP_MARK(c, 3);
+  if (kh == 0) {
+    bf16* kc = p.kcache + (size_t)layer * p.T * 256;
+    bf16* vc = p.vcache + (size_t)layer * p.T * 256;
+#pragma unroll
+    for (int t = 0; t < NQ; ++t) {
+      const int n = 8 * (c.cta + t * p.G) + 2 * (c.lane & 3);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int r = 16 * mi + (c.lane >> 2) + 8 * h;
+        if (r >= p.S) continue;
+        const float f = c.fs[r];
+        const float v0 = f * acc[t][2 * h] + bias[t][0], v1 = f * acc[t][2 * h + 1] + bias[t][1];
+        const float2 cssn = c.rope[(t * 4 + (c.lane & 3)) * 64 + r];
+        const uint32_t o = pack_bf16x2(v0 * cssn.x - v1 * cssn.y, v1 * cssn.x + v0 * cssn.y);
+        if (n < 2048) *reinterpret_cast<uint32_t*>(p.q + (size_t)r * 2048 + n) = o;
+        else if (n < 2304) *reinterpret_cast<uint32_t*>(kc + (size_t)(p.P + r) * 256 + (n - 2048)) = o;
+        else *reinterpret_cast<uint32_t*>(vc + (size_t)(p.P + r) * 256 + (n - 2304)) = o;
+      }
+    }
+  }
+  XP_MARK(c, 4);
   return ok;
+}
+__device__ __forceinline__ int qkv_tile_count(int cta, int G) {
+  return (cta + 2 * G < 320) ? 3 : ((cta + G < 320) ? 2 : (cta < 320 ? 1 : 0));
+}
+__device__ __forceinline__ bool phase_qkv(Ctx& c, int step, int layer) {
+  const int nq = qkv_tile_count(c.cta, c.p->G);
+  XP_MARK(c, 0);
+  if (nq == 3) return qkv_tiles<3>(c, step, layer);
+  if (nq == 2) return qkv_tiles<2>(c, step, layer);
+  if (nq == 1) return qkv_tiles<1>(c, step, layer);
+  return true;
 }
 
 // GeGLU: hidden[:, 32c..32c+31] = gelu(f * (xb @ Wg) + bg) * (f * (xb @ Wu) + bu), four (gate, up) tile pairs per CTA.
@@ -527,59 +577,69 @@ __device__ __forceinline__ bool phase_geglu(Ctx& c, int step, int layer) {
   if (c.cta >= N_OWNERS) return true;
   bool ok = true;
   XP_MARK(c, 60);
-  load_a_resident(c, p.xb, p.S, 1024, 1024);
-  compute_fs(c);
-  cp_async_wait<0>();
-  cbar();
-  XP_MARK(c, 61);
   const int mi = c.warp & 3, kh = c.warp >> 2;
-  const float* bg = p.pi05 ? p.sw_gate + ((size_t)step * p.nl + layer) * 4096 : nullptr;
-  const float* bu = p.pi05 ? p.sw_up + ((size_t)step * p.nl + layer) * 4096 : nullptr;
-  for (int i = 0; i < 4; ++i) {
-    uint32_t sl[2];
-    sl[0] = acquire_chunk(c, c.chunk_g, &ok);
-    sl[1] = acquire_chunk(c, c.chunk_g + 1, &ok);
-    XP_MARK(c, 62 + 4 * i);
-    float acc[2][4];
-    if (ok) mma_resident<2>(c, sl, p.S, 32, acc);
-    XP_MARK(c, 63 + 4 * i);
-    release_chunk(c, c.chunk_g);
-    release_chunk(c, c.chunk_g + 1);
-    c.chunk_g += 2;
-    reduce_khalves<2>(c, i & 1, acc);
-    XP_MARK(c, 64 + 4 * i);
-    if (kh == 0) {
-      const int n = 32 * c.cta + 8 * i + 2 * (c.lane & 3);
-      const float g0 = bg ? bg[n] : 0.f, g1 = bg ? bg[n + 1] : 0.f, u0 = bu ? bu[n] : 0.f, u1 = bu ? bu[n + 1] : 0.f;
+  float bg[4][2], bu[4][2];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int r = 16 * mi + (c.lane >> 2) + 8 * h;
-        if (r >= p.S) continue;
-        const float f = c.fs[r];
-        const float h0 = gelu_tanh_f(f * acc[0][2 * h] + g0) * (f * acc[1][2 * h] + u0);
-        const float h1 = gelu_tanh_f(f * acc[0][2 * h + 1] + g1) * (f * acc[1][2 * h + 1] + u1);
-        *reinterpret_cast<uint32_t*>(p.hidden + (size_t)r * 4096 + n) = pack_bf16x2(h0, h1);
+  for (int i = 0; i < 4; ++i) { bg[i][0] = bg[i][1] = bu[i][0] = bu[i][1] = 0.f; }
+  if (p.pi05 && kh == 0) {
+    const float* g = p.sw_gate + ((size_t)step * p.nl + layer) * 4096;
+    const float* u = p.sw_up + ((size_t)step * p.nl + layer) * 4096;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int n = 32 * c.cta + 8 * i + 2 * (c.lane & 3);
+      bg[i][0] = g[n]; bg[i][1] = g[n + 1]; bu[i][0] = u[n]; bu[i][1] = u[n + 1];
+    }
+  }
+  const unsigned long long fv = fs_issue(c);
+#pragma unroll
+  for (int pass = 0; pass < 2; ++pass) {     // chunks (gate, up, gate, up) of pairs 2 pass, 2 pass + 1 share the A fragments
+    uint32_t sl[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) sl[j] = acquire_chunk(c, c.chunk_g + j, &ok);
+    float acc[4][4];
+    mma_resident<4>(c, sl, p.S, c.a_g, acc, &ok);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) release_chunk(c, c.chunk_g + j);
+    c.chunk_g += 4;
+    if (pass == 0) fs_finish(c, fv);
+    reduce_khalves<4>(c, pass == 1, acc);   // the barrier inside also publishes fs
+    XP_MARK(c, 61 + pass);
+    if (kh == 0) {
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int i = 2 * pass + q;
+        const int n = 32 * c.cta + 8 * i + 2 * (c.lane & 3);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int r = 16 * mi + (c.lane >> 2) + 8 * h;
+          if (r >= p.S) continue;
+          const float f = c.fs[r];
+          const float h0 = gelu_tanh_f(f * acc[2 * q][2 * h] + bg[i][0]) * (f * acc[2 * q + 1][2 * h] + bu[i][0]);
+          const float h1 = gelu_tanh_f(f * acc[2 * q][2 * h + 1] + bg[i][1]) * (f * acc[2 * q + 1][2 * h + 1] + bu[i][1]);
+          *reinterpret_cast<uint32_t*>(p.hidden + (size_t)r * 4096 + n) = pack_bf16x2(h0, h1);
+        }
       }
     }
-    XP_MARK(c, 65 + 4 * i);
   }
+  a_release4(c);
+  XP_MARK(c, 65);
   return ok;
 }
 
 // Attention-out (K = 2048) and MLP-down (K = 4096) projections with the residual add.
-__device__ __forceinline__ bool phase_resid(Ctx& c, const bf16* a_src, int K, const float* gate, const float* mscale) {
+__device__ __forceinline__ bool phase_resid(Ctx& c, int K, const float* gate, const float* mscale) {
   const Params& p = *c.p;
-  if (c.cta >= N_OWNERS) return true;
+  ssq_rotate(c);
+  if (c.cta >= N_OWNERS) { ++c.pk; return true; }
+  XP_MARK(c, K == 2048 ? 20 : 40);
+  const ResidEpi e = make_resid(c, p.S, 0, true, nullptr, gate, mscale);
   float acc[1][4];
-  const bool ok = mma_streamed(c, a_src, p.S, K, acc);
-  reduce_khalves<1>(c, 0, acc);
-  XP_MARK(c, K == 2048 ? 38 : 58);
-  if ((c.warp >> 2) == 0) {
-    ResidEpi e;
-    e.rows = p.S; e.row_off = 0; e.accumulate = true; e.bias = nullptr; e.gate = gate; e.mscale = mscale;
-    epi_resid(c, e, acc[0]);
-  }
-  XP_MARK(c, K == 2048 ? 39 : 59);
+  const bool ok = mma_streamed(c, p.S, K, acc);
+  XP_MARK(c, K == 2048 ? 21 : 41);
+  reduce_khalves<1>(c, false, acc);
+  if ((c.warp >> 2) == 0) epi_resid(c, e, acc[0]);
+  XP_MARK(c, K == 2048 ? 22 : 42);
+  ++c.pk;
   return ok;
 }
 
@@ -589,16 +649,15 @@ __device__ __forceinline__ bool phase_out(Ctx& c, int step) {
   if (c.cta >= 4) return true;
   bool ok = true;
   const int off = p.pi05 ? 0 : 1;
-  load_a_resident(c, p.xb + (size_t)off * 1024, p.C, 1024, 1024);
-  compute_fs(c);
+  const unsigned long long fv = fs_issue(c);
   const uint32_t sl = acquire_chunk(c, c.chunk_g, &ok);
-  cp_async_wait<0>();
-  cbar();
   float acc[1][4];
-  if (ok) mma_resident<1>(c, &sl, p.C, 32, acc);
+  mma_resident<1>(c, &sl, p.C, c.a_g, acc, &ok);
   release_chunk(c, c.chunk_g);
+  a_release4(c);
   c.chunk_g += 1;
-  reduce_khalves<1>(c, 0, acc);
+  fs_finish(c, fv);
+  reduce_khalves<1>(c, false, acc);
   if ((c.warp >> 2) == 0) {
     const int mi = c.warp & 3;
     const int n = 8 * c.cta + 2 * (c.lane & 3);
@@ -630,36 +689,25 @@ __device__ __forceinline__ bool phase_out(Ctx& c, int step) {
 // <= 96 keys; softmax within the split; unnormalised output and (max, sum) go to the merge buffers.
 // Visibility (pi0_infer.py:1069-1095, pi05_infer.py:382-416): key j is visible if (j < valid_len or j >= P), and the
 // first `restrict` rows (the Pi0 state token's 8 heads) only see keys j <= P.
-__device__ __forceinline__ void phase_attention(Ctx& c, int layer) {
+// Shared memory: K tiles [4 dim blocks][kps keys][128 B] at 0, V tiles the same at ATT_V_OFF, Q tiles [4][32][128 B]
+// at ATT_Q_OFF, all written by TMA with the 128-byte swizzle.
+__device__ __forceinline__ bool phase_attention(Ctx& c, int layer) {
   const Params& p = *c.p;
   const int n_items = p.att_nrb * p.att_ks;
-  if (c.cta >= n_items) return;
+  if (c.cta >= n_items) return true;
   const int rb = c.cta / p.att_ks, sp = c.cta - rb * p.att_ks;
   const int R = p.S * 8;
   const int r0 = rb * ATT_ROWS;
   const int key0 = sp * p.att_kps;
   const int nk = max(0, min(p.att_kps, p.T - key0));          // real keys of this split
   const int nkp = (nk + 15) & ~15;                            // padded to the mma K step
-  const uint32_t sQ = c.sbase + A_BYTES, sK = c.sbase, sV = c.sbase + ATT_MAX_KEYS * 512;
-  const uint32_t sP = c.sbase + 2 * ATT_MAX_KEYS * 512;       // bf16 [32][104] (pitch 208 B)
-  float* red = reinterpret_cast<float*>(c.sptr + 2 * ATT_MAX_KEYS * 512 + 32 * 208);   // rmax[4][32], rsum[4][32]
-  const bf16* kc = p.kcache + ((size_t)layer * p.T + key0) * 256;
-  const bf16* vc = p.vcache + ((size_t)layer * p.T + key0) * 256;
-  for (int idx = c.tid; idx < ATT_ROWS * 32; idx += CTHREADS) {
-    const int row = idx >> 5, ch = idx & 31;
-    const bool v = r0 + row < R;
-    cp_async16(sQ + swz(row, ch, 512), p.q + (size_t)(v ? r0 + row : 0) * 256 + ch * 8, v ? 16 : 0);
-  }
-  for (int idx = c.tid; idx < nkp * 32; idx += CTHREADS) {
-    const int row = idx >> 5, ch = idx & 31;
-    const bool v = row < nk;
-    cp_async16(sK + swz(row, ch, 512), kc + (size_t)(v ? row : 0) * 256 + ch * 8, v ? 16 : 0);
-    cp_async16(sV + swz(row, ch, 512), vc + (size_t)(v ? row : 0) * 256 + ch * 8, v ? 16 : 0);
-  }
+  const uint32_t sQ = c.sbase + ATT_Q_OFF, sK = c.sbase, sV = c.sbase + ATT_V_OFF;
+  const uint32_t kv_tile = (uint32_t)p.att_kps * 128;
+  const uint32_t sP = c.sbase + A_BYTES;                      // bf16 [32][104] (pitch 208 B)
+  float* red = reinterpret_cast<float*>(c.sptr + A_BYTES + 32 * 208);   // rmax[4][32], rsum[4][32]
   XP_MARK(c, 10);
-  cp_async_commit();
-  cp_async_wait<0>();
-  cbar();
+  const bool ok = wait_bar(c, c.att_full, c.att_n & 1u);
+  ++c.att_n;
   XP_MARK(c, 11);
 
   const int mi = c.warp & 1, grp = c.warp >> 1;     // 16-row tile, key group (S) / 64-dim group (O)
@@ -672,26 +720,41 @@ __device__ __forceinline__ void phase_attention(Ctx& c, int layer) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) s[t][j] = 0.f;
   const int n_kt = nkp >> 3;
-  {
+  if (ok) {
     const int qrow = 16 * mi + (c.lane & 15);
-    const uint32_t q_row = sQ + qrow * 512;
-    const int qx = qrow & 7, hi = c.lane >> 4;
-#pragma unroll 2
-    for (int k2 = 0; k2 < 8; ++k2) {      // two k16 steps per iteration (32 dims)
-      uint32_t a0, a1, a2, a3, e0, e1, e2, e3;
-      ldsm_x4(q_row + (uint32_t)(((4 * k2 + hi) ^ qx) << 4), a0, a1, a2, a3);
-      ldsm_x4(q_row + (uint32_t)(((4 * k2 + 2 + hi) ^ qx) << 4), e0, e1, e2, e3);
+    const int hi = c.lane >> 4;
+    struct SF { uint32_t a[8]; uint32_t b[3][4]; };
+    auto load = [&](SF& f, int k2) {     // two k16 steps (32 dims): dims block k2 >> 1, chunks 4 (k2 & 1) ..
+      const uint32_t qt = sQ + (uint32_t)(k2 >> 1) * 4096;
+      const int c0 = 4 * (k2 & 1) + hi;
+      ldsm_x4(qt + swz128(qrow, c0), f.a[0], f.a[1], f.a[2], f.a[3]);
+      ldsm_x4(qt + swz128(qrow, c0 + 2), f.a[4], f.a[5], f.a[6], f.a[7]);
 #pragma unroll
       for (int t = 0; t < 3; ++t) {
         const int kt = grp + 4 * t;
         if (kt < n_kt) {
           const int krow = 8 * kt + (c.lane & 7);
-          uint32_t b0, b1, b2, b3;
-          ldsm_x4(sK + krow * 512 + (uint32_t)(((4 * k2 + (c.lane >> 3)) ^ (krow & 7)) << 4), b0, b1, b2, b3);
-          mma16816(s[t], a0, a1, a2, a3, b0, b1);
-          mma16816(s[t], e0, e1, e2, e3, b2, b3);
+          ldsm_x4(sK + (uint32_t)(k2 >> 1) * kv_tile + swz128(krow, 4 * (k2 & 1) + (c.lane >> 3)), f.b[t][0], f.b[t][1], f.b[t][2], f.b[t][3]);
         }
       }
+    };
+    auto mma = [&](const SF& f) {
+#pragma unroll
+      for (int t = 0; t < 3; ++t) {
+        if (grp + 4 * t < n_kt) {
+          mma16816(s[t], f.a[0], f.a[1], f.a[2], f.a[3], f.b[t][0], f.b[t][1]);
+          mma16816(s[t], f.a[4], f.a[5], f.a[6], f.a[7], f.b[t][2], f.b[t][3]);
+        }
+      }
+    };
+    SF f0, f1;
+    load(f0, 0);
+#pragma unroll 1
+    for (int k2 = 0; k2 < 8; k2 += 2) {
+      load(f1, k2 + 1);
+      mma(f0);
+      if (k2 + 2 < 8) load(f0, k2 + 2);
+      mma(f1);
     }
   }
   XP_MARK(c, 12);
@@ -749,26 +812,39 @@ __device__ __forceinline__ void phase_attention(Ctx& c, int layer) {
   }
   cbar();
   XP_MARK(c, 13);
-  // ---- O = P V for dims 64 grp .. 64 grp + 63 ----
+  // ---- O = P V for dims 64 grp .. 64 grp + 63 (one 64-dim V block per warp group) ----
   float o[8][4];
 #pragma unroll
   for (int t = 0; t < 8; ++t)
 #pragma unroll
     for (int j = 0; j < 4; ++j) o[t][j] = 0.f;
-  {
+  if (ok) {
     const int prow = 16 * mi + (c.lane & 15);
-    for (int ks = 0; ks < (nkp >> 4); ++ks) {
-      uint32_t a0, a1, a2, a3;
-      ldsm_x4(sP + prow * 208 + (uint32_t)((2 * ks + (c.lane >> 4)) << 4), a0, a1, a2, a3);
+    const uint32_t vt = sV + (uint32_t)grp * kv_tile;
+    struct PF { uint32_t a[4]; uint32_t b[4][4]; };
+    auto load = [&](PF& f, int ks) {
+      ldsm_x4(sP + prow * 208 + (uint32_t)((2 * ks + (c.lane >> 4)) << 4), f.a[0], f.a[1], f.a[2], f.a[3]);
       const int vrow = 16 * ks + (c.lane & 7) + 8 * ((c.lane >> 3) & 1);
 #pragma unroll
-      for (int t2 = 0; t2 < 4; ++t2) {     // two 8-dim tiles per ldmatrix
-        const int ch = 8 * grp + 2 * t2 + (c.lane >> 4);
-        uint32_t b0, b1, b2, b3;
-        ldsm_x4_t(sV + vrow * 512 + (uint32_t)((ch ^ (vrow & 7)) << 4), b0, b1, b2, b3);
-        mma16816(o[2 * t2], a0, a1, a2, a3, b0, b1);
-        mma16816(o[2 * t2 + 1], a0, a1, a2, a3, b2, b3);
+      for (int t2 = 0; t2 < 4; ++t2)     // two 8-dim tiles per ldmatrix
+        ldsm_x4_t(vt + swz128(vrow, 2 * t2 + (c.lane >> 4)), f.b[t2][0], f.b[t2][1], f.b[t2][2], f.b[t2][3]);
+    };
+    auto mma = [&](const PF& f) {
+#pragma unroll
+      for (int t2 = 0; t2 < 4; ++t2) {
+        mma16816(o[2 * t2], f.a[0], f.a[1], f.a[2], f.a[3], f.b[t2][0], f.b[t2][1]);
+        mma16816(o[2 * t2 + 1], f.a[0], f.a[1], f.a[2], f.a[3], f.b[t2][2], f.b[t2][3]);
       }
+    };
+    const int n_ks = nkp >> 4;
+    PF f0, f1;
+    if (n_ks > 0) load(f0, 0);
+#pragma unroll 1
+    for (int ks = 0; ks < n_ks; ks += 2) {
+      if (ks + 1 < n_ks) load(f1, ks + 1);
+      mma(f0);
+      if (ks + 2 < n_ks) load(f0, ks + 2);
+      if (ks + 1 < n_ks) mma(f1);
     }
   }
   XP_MARK(c, 14);
@@ -789,31 +865,56 @@ __device__ __forceinline__ void phase_attention(Ctx& c, int layer) {
     __stcg(reinterpret_cast<float2*>(p.att_stat + ((size_t)c.cta * ATT_ROWS + rl) * 2), make_float2(mm, l));
   }
   XP_MARK(c, 15);
+  return ok;
 }
 
-// Suffix attention, part 2: rows are dealt round-robin to the CTAs; thread d merges dimension d over the key splits.
+// Suffix attention, part 2: rows are dealt round-robin to the CTAs; a warp pair merges one row (each lane 4 dims) over
+// the key splits, with every load of a batch of 8 splits issued before the first use.
 __device__ __forceinline__ void phase_attention_merge(Ctx& c) {
   const Params& p = *c.p;
   const int R = p.S * 8, ks = p.att_ks;
+  const int slot = c.warp >> 1, half = c.warp & 1;
   XP_MARK(c, 16);
-  for (int r = c.cta; r < R; r += p.G) {
+  for (int r = c.cta + slot * p.G; r < R; r += 4 * p.G) {
     const int rb = r / ATT_ROWS, rl = r - rb * ATT_ROWS;
-    float mx = -INFINITY;
-    for (int s = 0; s < ks; ++s) mx = fmaxf(mx, __ldcg(p.att_stat + ((size_t)(rb * ks + s) * ATT_ROWS + rl) * 2));
-    float L = 0.f, acc = 0.f;
-    for (int s = 0; s < ks; ++s) {
-      const float2 st = __ldcg(reinterpret_cast<const float2*>(p.att_stat + ((size_t)(rb * ks + s) * ATT_ROWS + rl) * 2));
-      const float w = st.x == -INFINITY ? 0.f : exp2f(st.x - mx);
-      L += w * st.y;
-      acc += w * __ldcg(p.att_part + ((size_t)(rb * ks + s) * ATT_ROWS + rl) * 256 + c.tid);
+    const float2* st = reinterpret_cast<const float2*>(p.att_stat) + (size_t)rb * ks * ATT_ROWS + rl;
+    const float4* pt = reinterpret_cast<const float4*>(p.att_part + ((size_t)rb * ks * ATT_ROWS + rl) * 256 + 128 * half) + c.lane;
+    float mx = -INFINITY, L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < ks; s0 += 8) {
+      float2 sv[8];
+      float4 pv[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const bool in = s0 + i < ks;
+        sv[i] = in ? __ldcg(st + (size_t)(s0 + i) * ATT_ROWS) : make_float2(-INFINITY, 0.f);
+        pv[i] = in ? __ldcg(pt + (size_t)(s0 + i) * ATT_ROWS * 64) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      float bm = mx;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) bm = fmaxf(bm, sv[i].x);
+      // rescale what has been accumulated so far to the new maximum (first batch: nothing accumulated, factor irrelevant)
+      const float resc = (mx == -INFINITY) ? 0.f : exp2f(mx - bm);
+      L *= resc; acc.x *= resc; acc.y *= resc; acc.z *= resc; acc.w *= resc;
+      mx = bm;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float w = sv[i].x == -INFINITY ? 0.f : exp2f(sv[i].x - mx);
+        L += w * sv[i].y;
+        acc.x += w * pv[i].x; acc.y += w * pv[i].y; acc.z += w * pv[i].z; acc.w += w * pv[i].w;
+      }
     }
-    p.attn[(size_t)r * 256 + c.tid] = __float2bfloat16(acc / L);
+    const float inv = 1.0f / L;
+    uint2 o;
+    o.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+    o.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(p.attn + (size_t)r * 256 + 128 * half + 4 * c.lane) = o;
   }
   XP_MARK(c, 17);
 }
 
 // ---- weight stream (warp 8, one lane) ---------------------------------------------------------------------------------------
-__device__ __forceinline__ void producer_loop(Ctx& c) {
+__device__ __forceinline__ void weight_producer_loop(Ctx& c) {
   const Params& p = *c.p;
   const uint4* base = p.wstream + (size_t)c.cta * p.chunks_per_cta * (CHUNK_BYTES / 16);
   const uint64_t pol = policy_evict_first();
@@ -822,13 +923,13 @@ __device__ __forceinline__ void producer_loop(Ctx& c) {
   auto push = [&](int idx) {
     if (!ok) return;
     const unsigned int s = g % NSLOT;
-    if (g >= NSLOT) ok = wait_bar(c, c.empty_bar + 8 * s, ((g / NSLOT) - 1) & 1u);
+    if (g >= NSLOT) ok = wait_bar(c, c.w_empty + 8 * s, ((g / NSLOT) - 1) & 1u);
     if (!ok) return;
-    mbar_expect_tx(c.full_bar + 8 * s, CHUNK_BYTES);
-    bulk_g2s(c.sbase + RING_OFF + s * CHUNK_BYTES, base + (size_t)idx * (CHUNK_BYTES / 16), CHUNK_BYTES, c.full_bar + 8 * s, pol);
+    mbar_expect_tx(c.w_full + 8 * s, CHUNK_BYTES);
+    bulk_g2s(c.sbase + RING_OFF + s * CHUNK_BYTES, base + (size_t)idx * (CHUNK_BYTES / 16), CHUNK_BYTES, c.w_full + 8 * s, pol);
     ++g;
   };
-  const int nq = (c.cta + 2 * p.G < 320) ? 3 : ((c.cta + p.G < 320) ? 2 : (c.cta < 320 ? 1 : 0));
+  const int nq = qkv_tile_count(c.cta, p.G);
   const bool owner = c.cta < N_OWNERS;
   for (int step = 0; step < p.nsteps && ok; ++step) {
     if (!p.pi05 && owner) push(p.misc_base);
@@ -842,9 +943,94 @@ __device__ __forceinline__ void producer_loop(Ctx& c) {
   if (!ok) {
     // give the copies still in flight time to land before the CTA can retire (bounded)
     for (unsigned int i = (g > NSLOT ? g - NSLOT : 0); i < g; ++i) {
-      const uint32_t bar = c.full_bar + 8 * (i % NSLOT);
+      const uint32_t bar = c.w_full + 8 * (i % NSLOT);
       for (int tries = 0; tries < 20000 && !mbar_try_wait(bar, (i / NSLOT) & 1u); ++tries) __nanosleep(50);
     }
+  }
+}
+
+// ---- activation loads (warp 9, one lane) ----------------------------------------------------------------------------------------
+// Follows the same phase sequence as the MMA warps.  Phase j may read what other CTAs wrote once j grid barriers have
+// been passed (thread 0 publishes the count); the loads of a phase are issued at once, as far as the four stages reach,
+// and the rest as stages are handed back.
+__device__ __forceinline__ void activation_producer_loop(Ctx& c) {
+  const Params& p = *c.p;
+  const uint64_t pol = policy_evict_last();
+  unsigned int g = 0, att_n = 0;
+  int phase = 0;
+  bool ok = true;
+  auto wait_go = [&](int needed) {
+    if (!ok) return;
+    const uint64_t t0 = globaltimer_ns();
+    unsigned int spins = 0;
+    while (*c.go_count < needed) {
+      __nanosleep(32);   // a busy loop here would take issue slots from the MMA warps on this scheduler
+      if ((++spins & 63u) == 0) {
+        if (poll_abort(c)) { ok = false; return; }
+        if (globaltimer_ns() - t0 > VLA_WAIT_LIMIT_NS) { raise_timeout(c); ok = false; return; }
+      }
+    }
+    __threadfence();
+    fence_proxy_async_all();   // the rows were written through the generic proxy, the copies below read through the async one
+  };
+  auto stages = [&](const CUtensorMap* tm, int n_stages, int row0, int box_rows) {
+    for (int st = 0; st < n_stages && ok; ++st) {
+      const unsigned int s = g & 3u;
+      if (g >= 4) ok = wait_bar(c, c.a_empty + 8 * s, ((g >> 2) - 1) & 1u);
+      if (!ok) return;
+      mbar_expect_tx(c.a_full + 8 * s, (uint32_t)(4 * box_rows * 128));
+#pragma unroll
+      for (int t = 0; t < 4; ++t)
+        tma_load_2d(c.sbase + s * STAGE_BYTES + t * TILE_BYTES, tm, c.a_full + 8 * s, st * 256 + t * 64, row0, pol);
+      ++g;
+    }
+  };
+  const int nq = qkv_tile_count(c.cta, p.G);
+  const bool owner = c.cta < N_OWNERS;
+  const int n_items = p.att_nrb * p.att_ks;
+  for (int step = 0; step < p.nsteps && ok; ++step) {
+    ++phase;                                        // action in-projection: loads its own rows
+    if (!p.pi05) {                                  // action MLP
+      if (owner) { wait_go(phase); stages(&p.tm_act, 4, 0, p.C); }
+      ++phase;
+    }
+    for (int l = 0; l < p.nl && ok; ++l) {
+      if (nq > 0) { wait_go(phase); stages(&p.tm_xb, 4, 0, p.S); }
+      ++phase;
+      if (c.cta < n_items) {                        // attention: K, V and Q tiles of this CTA's work item
+        wait_go(phase);
+        if (!ok) break;
+        // the four stages of the QKV phase have been handed back by every warp before the barrier just passed
+        const int rb = c.cta / p.att_ks, sp = c.cta - rb * p.att_ks;
+        const int row_k = l * p.T + sp * p.att_kps;
+        const uint32_t kv_tile = (uint32_t)p.att_kps * 128;
+        mbar_expect_tx(c.att_full, 4 * 4096 + 8 * kv_tile);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          tma_load_2d(c.sbase + t * kv_tile, &p.tm_k, c.att_full, 64 * t, row_k, pol);
+          tma_load_2d(c.sbase + ATT_V_OFF + t * kv_tile, &p.tm_v, c.att_full, 64 * t, row_k, pol);
+          tma_load_2d(c.sbase + ATT_Q_OFF + t * 4096, &p.tm_q, c.att_full, 64 * t, rb * ATT_ROWS, pol);
+        }
+        ++att_n;
+      }
+      ++phase;
+      ++phase;                                      // merge: reads global memory directly
+      if (owner) { wait_go(phase); stages(&p.tm_attn, 8, 0, p.S); }
+      ++phase;
+      if (owner) { wait_go(phase); stages(&p.tm_xb, 4, 0, p.S); }
+      ++phase;
+      if (owner) { wait_go(phase); stages(&p.tm_hidden, 16, 0, p.S); }
+      ++phase;
+    }
+    if (c.cta < 4) { wait_go(phase); stages(&p.tm_xb, 4, p.pi05 ? 0 : 1, p.S); }
+    ++phase;
+  }
+  if (!ok) {
+    // bounded wait for copies still in flight
+    for (unsigned int i = (g > 4 ? g - 4 : 0); i < g; ++i)
+      for (int tries = 0; tries < 20000 && !mbar_try_wait(c.a_full + 8 * (i & 3u), (i >> 2) & 1u); ++tries) __nanosleep(50);
+    if (att_n > 0)
+      for (int tries = 0; tries < 20000 && !mbar_try_wait(c.att_full, (att_n - 1) & 1u); ++tries) __nanosleep(50);
   }
 }
 
@@ -852,19 +1038,27 @@ __device__ __forceinline__ void producer_loop(Ctx& c) {
 __global__ void __launch_bounds__(THREADS, 1) expert_persistent_kernel(const __grid_constant__ Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t pad = (128u - (raw & 127u)) & 127u;
+  const uint32_t pad = (1024u - (raw & 1023u)) & 1023u;
   Ctx c;
   c.p = &p;
   c.sbase = raw + pad;
   c.sptr = smem_raw + pad;
   uint8_t* persist = c.sptr + PERSIST_OFF;
-  c.full_bar = c.sbase + PERSIST_OFF;
-  c.empty_bar = c.full_bar + 8 * NSLOT;
-  c.s_abort = reinterpret_cast<volatile int*>(persist + 128);
-  c.fs = reinterpret_cast<float*>(persist + 256);
-  c.xs = reinterpret_cast<float*>(persist + 512);        // 64 x 8 floats = 2 KB
-  c.sttok = reinterpret_cast<float*>(persist + 2560);
+  c.w_full = c.sbase + PERSIST_OFF;
+  c.w_empty = c.w_full + 8 * NSLOT;
+  c.a_full = c.w_empty + 8 * NSLOT;
+  c.a_empty = c.a_full + 8 * N_ASTAGE;
+  c.att_full = c.a_empty + 8 * N_ASTAGE;
+  c.go_count = reinterpret_cast<volatile int*>(persist + 256);
+  c.s_abort = reinterpret_cast<volatile int*>(persist + 260);
+  c.fs = reinterpret_cast<float*>(persist + 512);
+  c.xs = reinterpret_cast<float*>(persist + 768);        // 64 x 8 floats = 2 KB
+  c.sttok = reinterpret_cast<float*>(persist + 2816);
+  c.rope = reinterpret_cast<float2*>(persist + 3072);    // 3 x 4 x 64 float2 = 6 KB
+  c.pk = 0;
   c.chunk_g = 0;
+  c.a_g = 0;
+  c.att_n = 0;
   c.bar_epoch = 0;
   c.fine = false;
   c.cta = blockIdx.x;
@@ -875,17 +1069,41 @@ __global__ void __launch_bounds__(THREADS, 1) expert_persistent_kernel(const __g
   c.pos_base = p.pi05 ? (p.pos_base_ptr ? *p.pos_base_ptr : p.P - 1) : p.P;
   if (threadIdx.x == 0) {
     for (int s = 0; s < NSLOT; ++s) {
-      mbar_init(c.full_bar + 8 * s, 1);
-      mbar_init(c.empty_bar + 8 * s, 8);
+      mbar_init(c.w_full + 8 * s, 1);
+      mbar_init(c.w_empty + 8 * s, 8);
     }
+    for (int s = 0; s < N_ASTAGE; ++s) {
+      mbar_init(c.a_full + 8 * s, 1);
+      mbar_init(c.a_empty + 8 * s, 8);
+    }
+    mbar_init(c.att_full, 1);
+    *c.go_count = 0;
     *c.s_abort = 0;
     mbar_fence_init();
   }
   for (int i = threadIdx.x; i < 64 * 8; i += THREADS) c.xs[i] = 0.f;
+  for (int i = threadIdx.x; i < 3 * 4 * 64; i += THREADS) {   // rotary factors of this CTA's QKV feature pairs (V: identity)
+    const int r = i & 63, pair = (i >> 6) & 3, t = i >> 8;
+    const int n = 8 * (c.cta + t * p.G) + 2 * pair;
+    float2 v = make_float2(1.f, 0.f);
+    if (n < 2304 && r < p.S) {
+      const int pos = c.pos_base + r, fi = (n & 255) >> 1;
+      v = make_float2(p.rope_cos[pos * 128 + fi], p.rope_sin[pos * 128 + fi]);
+    }
+    c.rope[i] = v;
+  }
+  if (threadIdx.x == 32 * 9) {
+    tma_prefetch_desc(&p.tm_xb); tma_prefetch_desc(&p.tm_attn); tma_prefetch_desc(&p.tm_hidden);
+    tma_prefetch_desc(&p.tm_q); tma_prefetch_desc(&p.tm_k); tma_prefetch_desc(&p.tm_v);
+    if (!p.pi05) tma_prefetch_desc(&p.tm_act);
+  }
   __syncthreads();
 
   if (c.warp == 8) {
-    if (c.lane == 0) producer_loop(c);
+    if (c.lane == 0) weight_producer_loop(c);
+    __syncwarp();
+  } else if (c.warp == 9) {
+    if (c.lane == 0) activation_producer_loop(c);
     __syncwarp();
   } else {
     bool ok = true;
@@ -908,15 +1126,14 @@ __global__ void __launch_bounds__(THREADS, 1) expert_persistent_kernel(const __g
         ok = phase_qkv(c, step, l);
         ok = grid_barrier(c, ph++) && ok;
         if (!ok) break;
-        phase_attention(c, l);
-        ok = grid_barrier(c, ph++);
+        ok = phase_attention(c, l);
+        ok = grid_barrier(c, ph++) && ok;
         if (!ok) break;
         phase_attention_merge(c);
         ok = grid_barrier(c, ph++);
         if (!ok) break;
         const size_t sl = (size_t)step * p.nl + l;
-        ok = phase_resid(c, p.attn, 2048, p.pi05 ? p.style_attn + sl * 3072 + 2048 : nullptr,
-                         p.pi05 ? p.style_ffn + sl * 3072 : nullptr);
+        ok = phase_resid(c, 2048, p.pi05 ? p.style_attn + sl * 3072 + 2048 : nullptr, p.pi05 ? p.style_ffn + sl * 3072 : nullptr);
         ok = grid_barrier(c, ph++) && ok;
         if (!ok) break;
         ok = phase_geglu(c, step, l);
@@ -924,9 +1141,10 @@ __global__ void __launch_bounds__(THREADS, 1) expert_persistent_kernel(const __g
         if (!ok) break;
         const float* next_scale = nullptr;
         if (p.pi05) next_scale = (l + 1 < p.nl) ? p.style_attn + (sl + 1) * 3072 : p.style_fin + (size_t)step * 3072;
-        ok = phase_resid(c, p.hidden, 4096, p.pi05 ? p.style_ffn + sl * 3072 + 2048 : nullptr, next_scale);
+        ok = phase_resid(c, 4096, p.pi05 ? p.style_ffn + sl * 3072 + 2048 : nullptr, next_scale);
         ok = grid_barrier(c, ph++) && ok;
       }
+      c.fine = false;
       if (!ok) break;
       ok = phase_out(c, step);
       ok = grid_barrier(c, ph++) && ok;

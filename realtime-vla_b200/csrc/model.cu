@@ -33,7 +33,7 @@ thread_local std::string g_last_error;
 
 // The persistent action-expert kernel serves eligible handles by default when true; flags bit 5 selects it
 // explicitly, bit 4 refuses it.
-constexpr bool XP_DEFAULT_ON = false;
+constexpr bool XP_DEFAULT_ON = true;
 
 // ---------------------------------------------------------------------------------------------------
 // driver entry point for tensor-map encoding (no link-time dependency on libcuda)
@@ -476,7 +476,7 @@ struct vla_model {
   bool use_xp = false;
   int xp_G = 0, xp_chunks = 0;
   uint4* xp_stream = nullptr;
-  float *xp_ssq = nullptr, *xp_part = nullptr, *xp_stat = nullptr, *xp_sw_fin = nullptr;
+  float *xp_part = nullptr, *xp_stat = nullptr, *xp_sw_fin = nullptr;
   unsigned int* xp_sync = nullptr;
   unsigned long long* xp_trace = nullptr;
   xp::Params xp_params;
@@ -663,10 +663,9 @@ bool alloc_buffers(vla_model* m) {
     const size_t items = (size_t)m->xp_params.att_nrb * m->xp_params.att_ks;
     m->xp_chunks = m->nl * xp::CH_PER_LAYER + 2;
     ok &= m->dalloc(&m->xp_stream, (size_t)m->xp_G * m->xp_chunks * (xp::CHUNK_BYTES / 16));
-    ok &= m->dalloc(&m->xp_ssq, (size_t)xp::N_OWNERS * 64);
     ok &= m->dalloc(&m->xp_part, items * xp::ATT_ROWS * 256);
     ok &= m->dalloc(&m->xp_stat, items * xp::ATT_ROWS * 2);
-    ok &= m->dalloc(&m->xp_sync, 2);
+    ok &= m->dalloc(&m->xp_sync, 512);   // barrier counter, abort word, then (at byte 512) the sums of squares [3][64] u64
     ok &= m->dalloc(&m->xp_trace, 4096);
     ok &= m->dalloc(&m->xp_sw_fin, (size_t)10 * 32);
   }
@@ -903,7 +902,7 @@ cudaError_t launch_expert_persistent(vla_model* m, cudaStream_t st, unsigned lon
   auto kern = xp::expert_persistent_kernel;
   if (cudaError_t e = ensure_smem_attr(reinterpret_cast<const void*>(kern), xp::SMEM_BYTES); e != cudaSuccess) return e;
   // barrier counter and abort word start from zero at every launch
-  if (cudaError_t e = cudaMemsetAsync(m->xp_sync, 0, 2 * sizeof(unsigned int), st); e != cudaSuccess) return e;
+  if (cudaError_t e = cudaMemsetAsync(m->xp_sync, 0, 512 * sizeof(unsigned int), st); e != cudaSuccess) return e;
   xp::Params p = m->xp_params;
   p.trace = trace;
   cudaLaunchConfig_t cfg;
@@ -943,10 +942,20 @@ void plan_decoder_persistent(Plan& pl) {
     p.b_out = pl.vec("decoder_action_fused_out_proj_b");
   }
   p.noise = m->noise; p.noise_f32 = m->noise_f32; p.act = m->decoder_act; p.x_out = m->decoder_x; p.xb = m->decoder_xb;
-  p.ssq = m->xp_ssq; p.q = m->decoder_q; p.kcache = m->kcache; p.vcache = m->vcache; p.attn = m->decoder_attn;
+  p.ssq = reinterpret_cast<unsigned long long*>(m->xp_sync + 128); p.q = m->decoder_q; p.kcache = m->kcache; p.vcache = m->vcache; p.attn = m->decoder_attn;
   p.hidden = m->decoder_hidden; p.att_part = m->xp_part; p.att_stat = m->xp_stat;
   p.rope_cos = m->rope_cos; p.rope_sin = m->rope_sin;
   p.bar_ctr = m->xp_sync; p.status = m->d_status; p.trace = nullptr;
+  // activation operands come in by TMA: 64-wide K blocks of all rows, 128-byte swizzle
+  const bool maps_ok =
+      make_tmap(&p.tm_xb, m->decoder_xb, 1024, m->S, 1024, m->S, &pl.err) &&
+      make_tmap(&p.tm_act, m->decoder_act, 1024, m->C, 1024, m->C, &pl.err) &&
+      make_tmap(&p.tm_attn, m->decoder_attn, 2048, m->S, 2048, m->S, &pl.err) &&
+      make_tmap(&p.tm_hidden, m->decoder_hidden, 4096, m->S, 4096, m->S, &pl.err) &&
+      make_tmap(&p.tm_q, m->decoder_q, 256, m->S * 8, 256, xp::ATT_ROWS, &pl.err) &&
+      make_tmap(&p.tm_k, m->kcache, 256, (long long)m->nl * m->T, 256, p.att_kps, &pl.err) &&
+      make_tmap(&p.tm_v, m->vcache, 256, (long long)m->nl * m->T, 256, p.att_kps, &pl.err);
+  if (!maps_ok) { pl.ok = false; return; }
   pl.kernel([m](cudaStream_t st) { return launch_expert_persistent(m, st, nullptr); });
 }
 
