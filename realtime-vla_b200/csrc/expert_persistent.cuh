@@ -245,8 +245,14 @@ __device__ __forceinline__ void ssq_add(const Ctx& c, int token, float sq) {
 // NT feature tiles (their chunks at slot addresses sl[0..NT-1]) against the four activation stages a_g0..a_g0+3 (K = 1024);
 // warp (mi, kh) takes rows 16 mi.. and K half kh.  The loop is bound by shared-memory bandwidth (1 KB of A and NT x 512 B
 // of B per iteration and warp), so the more tiles share an A fragment the better.
-template <int NT>
-__device__ __forceinline__ void mma_resident(Ctx& c, const uint32_t* sl, int rows, unsigned int a_g0, float (&acc)[NT][4], bool* ok) {
+// QUARTERS (GeGLU, NT = 4): the four chunks of a pass are K quarters [4 tiles][8 k-step pairs][lane][16 B] in the stream
+// order q0, q2, q1, q3 (the two K halves are read concurrently by the kh = 0 and kh = 1 warps), and every warp hands a
+// pair of quarters back as soon as it is through its own, so that the weight stream refills the ring during the pass
+// instead of after it.  chunk_g0 = index of the first chunk of the pass.
+template <int NT, bool QUARTERS = false>
+__device__ __forceinline__ void mma_resident(Ctx& c, const uint32_t* sl, int rows, unsigned int a_g0, float (&acc)[NT][4], bool* ok,
+                                             unsigned int chunk_g0 = 0) {
+  static_assert(!QUARTERS || NT == 4, "the quarter layout holds four tiles per chunk");
   const int mi = c.warp & 3, kh = c.warp >> 2;
   float acc2[4] = {0.f, 0.f, 0.f, 0.f};   // a single tile alternates two accumulators to break the dependent chain
 #pragma unroll
@@ -255,11 +261,16 @@ __device__ __forceinline__ void mma_resident(Ctx& c, const uint32_t* sl, int row
     for (int j = 0; j < 4; ++j) acc[t][j] = 0.f;
   // every warp waits for the stages of its K half, also a warp without rows: the stages are then handed back in step
   if (!a_wait(c, a_g0 + 2 * kh) || !a_wait(c, a_g0 + 2 * kh + 1)) *ok = false;
-  if (16 * mi >= rows || !*ok) return;
+  if (16 * mi >= rows || !*ok) {
+    if (QUARTERS)
+      for (int j = 0; j < 4; ++j) release_chunk(c, chunk_g0 + j);
+    return;
+  }
   const int row = min(16 * mi + (c.lane & 15), rows - 1);
   const int hi = c.lane >> 4;
   const uint32_t lane_off = (uint32_t)c.lane * 16;
   const uint32_t a_off0 = swz128(row, hi), a_off1 = swz128(row, hi + 2), a_off2 = swz128(row, hi + 4), a_off3 = swz128(row, hi + 6);
+  uint32_t qchunk = 0;
 #pragma unroll 2
   for (int i = 0; i < 8; ++i) {          // one 64-wide K block (four k16 steps) per round
     const int kb = 8 * kh + i;
@@ -269,15 +280,26 @@ __device__ __forceinline__ void mma_resident(Ctx& c, const uint32_t* sl, int row
     ldsm_x4(tile + a_off1, a[4], a[5], a[6], a[7]);
     ldsm_x4(tile + a_off2, a[8], a[9], a[10], a[11]);
     ldsm_x4(tile + a_off3, a[12], a[13], a[14], a[15]);
+    // quarter q = kb / 4 is chunk ((q & 1) << 1) | (q >> 1) of the pass; it is waited for only when this warp gets to it
+    uint32_t qbase = 0;
+    if (QUARTERS) {
+      if ((i & 3) == 0) qchunk = acquire_chunk(c, chunk_g0 + ((kb >> 2) & 1) * 2 + (kb >> 3), ok);
+      qbase = qchunk + (uint32_t)((2 * kb) & 7) * 512 + lane_off;
+    }
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
-      const uint4 b0 = lds128(sl[t] + (uint32_t)(2 * kb) * 512 + lane_off);
-      const uint4 b1 = lds128(sl[t] + (uint32_t)(2 * kb + 1) * 512 + lane_off);
+      const uint32_t baddr = QUARTERS ? qbase + (uint32_t)t * 4096 : sl[t] + (uint32_t)(2 * kb) * 512 + lane_off;
+      const uint4 b0 = lds128(baddr);
+      const uint4 b1 = lds128(baddr + 512);
       float* second = NT == 1 ? acc2 : acc[t];
       mma16816(acc[t], a[0], a[1], a[2], a[3], b0.x, b0.y);
       mma16816(second, a[4], a[5], a[6], a[7], b0.z, b0.w);
       mma16816(acc[t], a[8], a[9], a[10], a[11], b1.x, b1.y);
       mma16816(second, a[12], a[13], a[14], a[15], b1.z, b1.w);
+    }
+    if (QUARTERS && (i & 3) == 3) {      // through a quarter: hand back the pair of quarters the two K halves just finished
+      release_chunk(c, chunk_g0 + (i >> 2) * 2);
+      release_chunk(c, chunk_g0 + (i >> 2) * 2 + 1);
     }
   }
   if (NT == 1) {
@@ -592,14 +614,9 @@ __device__ __forceinline__ bool phase_geglu(Ctx& c, int step, int layer) {
   }
   const unsigned long long fv = fs_issue(c);
 #pragma unroll
-  for (int pass = 0; pass < 2; ++pass) {     // chunks (gate, up, gate, up) of pairs 2 pass, 2 pass + 1 share the A fragments
-    uint32_t sl[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) sl[j] = acquire_chunk(c, c.chunk_g + j, &ok);
+  for (int pass = 0; pass < 2; ++pass) {     // tiles (gate, up, gate, up) of pairs 2 pass, 2 pass + 1 share the A fragments
     float acc[4][4];
-    mma_resident<4>(c, sl, p.S, c.a_g, acc, &ok);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) release_chunk(c, c.chunk_g + j);
+    mma_resident<4, true>(c, nullptr, p.S, c.a_g, acc, &ok, c.chunk_g);   // waits for and hands back its chunks quarter by quarter
     c.chunk_g += 4;
     if (pass == 0) fs_finish(c, fv);
     reduce_khalves<4>(c, pass == 1, acc);   // the barrier inside also publishes fs
@@ -1176,12 +1193,28 @@ __global__ void pack_chunk_kernel(const bf16* __restrict__ w, int Kp, int n_vali
 // All chunks of one expert layer: grid (CH_PER_LAYER, G).  Stream slot j of CTA c holds (K-major sources, layer l):
 //   j = 0..2   QKV feature tile c + j G (if < 320), K 0..1023
 //   j = 3..4   attention-out tile c, K half j - 3                      (c < N_OWNERS from here on)
-//   j = 5..12  MLP gate (odd offsets: up) tile 4 c + (j - 5) / 2
+//   j = 5..12  MLP gate / up in K quarters (see below)
 //   j = 13..16 MLP down tile c, K quarter j - 13
 __global__ void pack_layer_kernel(const bf16* __restrict__ w_qkv, const bf16* __restrict__ w_o, const bf16* __restrict__ w_gate,
                                   const bf16* __restrict__ w_up, const bf16* __restrict__ w_down, int layer, int chunks_per_cta,
                                   bf16* __restrict__ stream) {
   const int j = blockIdx.x, cta = blockIdx.y, G = gridDim.y;
+  bf16* dst = stream + ((size_t)cta * chunks_per_cta + (size_t)layer * CH_PER_LAYER + j) * (CHUNK_BYTES / 2);
+  if (j >= 5 && j < 13) {
+    // MLP gate/up: pass p = (j - 5) / 4 covers the (gate, up) pairs 2p, 2p + 1 of this CTA's 32 hidden features; the chunk
+    // holds K quarter q of the pass's four tiles (gate, up, gate, up): [tile][k-step pair (8)][lane][8 bf16].
+    // Stream order of the quarters within a pass: q0, q2, q1, q3.
+    if (cta >= N_OWNERS) return;
+    const int pass = (j - 5) >> 2, oi = (j - 5) & 3, q = ((oi & 1) << 1) | (oi >> 1);
+    for (int e = threadIdx.x; e < CHUNK_BYTES / 2; e += blockDim.x) {
+      const int jj = e & 7, lane = (e >> 3) & 31, spq = (e >> 8) & 7, t = e >> 11;
+      const int ks = 2 * spq + (jj >> 2);                                      // k16 step within the quarter
+      const int k = 256 * q + 16 * ks + 8 * ((jj & 3) >> 1) + 2 * (lane & 3) + (jj & 1);
+      const int n = 32 * cta + 8 * (2 * pass + (t >> 1)) + (lane >> 2);
+      dst[e] = ((t & 1) ? w_up : w_gate)[(size_t)n * 1024 + k];
+    }
+    return;
+  }
   const bf16* src;
   int Kp, n0, k0;
   if (j < 3) {
@@ -1191,10 +1224,8 @@ __global__ void pack_layer_kernel(const bf16* __restrict__ w_qkv, const bf16* __
   } else {
     if (cta >= N_OWNERS) return;
     if (j < 5) { src = w_o; Kp = 2048; n0 = 8 * cta; k0 = 1024 * (j - 3); }
-    else if (j < 13) { src = ((j - 5) & 1) ? w_up : w_gate; Kp = 1024; n0 = 32 * cta + 8 * ((j - 5) >> 1); k0 = 0; }
     else { src = w_down; Kp = 4096; n0 = 8 * cta; k0 = 1024 * (j - 13); }
   }
-  bf16* dst = stream + ((size_t)cta * chunks_per_cta + (size_t)layer * CH_PER_LAYER + j) * (CHUNK_BYTES / 2);
   for (int e = threadIdx.x; e < CHUNK_BYTES / 2; e += blockDim.x) {
     int nl, kl;
     chunk_elem_src(e, &nl, &kl);
