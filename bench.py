@@ -3,15 +3,20 @@ benchmark.py:17-33 of the reference; plus observations/s for the data-parallel s
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg1|cfg2|cfg3]
 
-One "step" = one forward of one observation.  The default workload is configuration 2 of BASELINE.json:
-Pi0, 3 views, 20 prompt tokens, chunk 50, 10 Euler steps, full depth, seeded random bf16 weights and inputs
-(no checkpoint or camera data exists offline).  N > 1 runs one independent replica per GPU (the path has no
-cross-observation exchange: weak scaling, no collective on the data path).
+One "step" = one forward of one observation.  The default workload is Pi0, 3 views, 20 prompt tokens, chunk 50,
+10 Euler steps, full depth, seeded random bf16 weights and inputs (no checkpoint or camera data exists offline).
+N > 1 runs one independent replica per GPU (the path has no cross-observation exchange: weak scaling, no collective
+on the data path).
 
 Prints one JSON line.  `value` is observations/s over all ranks, timed on the device over exactly K graph
 replays with the inputs resident in HBM; the weights streamed by every forward (5.2 GB) exceed L2 by 40x,
 so no L2 flush is needed between iterations.  `e2e` is the same through the host-memory entry point of the
 C ABI (pinned host buffers in, actions out, copies and synchronisation inside the timed region).
+`roofline` describes the stage that owns most of the forward, the action expert (one persistent kernel launch per
+forward, HBM-bound weight streaming); `roofline_prefix` the largest tensor-bound kernel (prefix GeGLU GEMM).
+`reference_triton` is the reference's own Triton forward, timed on the same GPU by its own benchmark script from an
+unmodified copy under baseline/_ref (in a subprocess, before the timed region); `throughput_cfg5` is the throughput
+configuration (32 observations per forward and GPU) measured in the same run.
 `--impl reference` times the fp32 CPU oracle (the reference has no CPU path of its own) on the host cores.
 """
 import argparse
@@ -44,9 +49,11 @@ WORKLOADS = {
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
-# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from the ncu
-# capture summarised under profiles/), keyed by workload; None until a capture exists.
-NCU_TRAFFIC_BYTES = {"cfg2": 144519168, "cfg1": None, "cfg3": None, "cfg4": None, "cfg5": None, "pi05_3v": None, "pi05_b32": None}   # profiles/gemm_sm100_geglu_prefix_p788.md
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture): the prefix GeGLU GEMM at
+# 788 tokens, and the persistent action-expert kernel (captured at reduced depth, scaled to 18 layers x 10 steps by
+# the layer-steps processed: its traffic is the weight stream, which grows in proportion).
+NCU_TRAFFIC_GEGLU = {"cfg2": 144519168}
+NCU_TRAFFIC_EXPERT = {}
 
 
 def peaks():
@@ -298,6 +305,95 @@ def decoder_stream(wl, decoder_ms):
             "unit": "GB/s", "frac": round(gbs / pk["hbm_gbs"], 4), "bound": "hbm"}
 
 
+def expert_stage_roofline(wl, infer, noise, reps=20):
+    """The action-expert stage (one persistent kernel launch per forward; per-operator launches for batched handles):
+    average duration over `reps` launches, CUDA events on the launching stream, K/V cache filled by a full forward
+    before; algorithmic bytes = weights + K/V rows streamed by the 10 Euler steps, against the measured HBM copy peak."""
+    noise_buf = infer.buffers["diffusion_noise"]
+    torch.cuda.synchronize()
+    for _ in range(3):
+        noise_buf.copy_(noise)
+        infer._engine.forward_stages(4)
+    total = 0.0
+    for _ in range(reps):
+        noise_buf.copy_(noise)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        infer._engine.forward_stages(4)
+        b.record()
+        torch.cuda.synchronize()
+        total += a.elapsed_time(b)
+    ms = total / reps
+    r = decoder_stream(wl, ms)
+    n_launch = infer._engine.stage_kernels()[2]
+    r.update(kernel="expert_persistent_kernel: action-expert stage, 10 Euler steps, %d launch%s per forward" % (n_launch, "" if n_launch == 1 else "es"),
+             ms_per_launch=round(ms, 4), bytes_per_launch=r.pop("bytes_per_forward"), traffic=NCU_TRAFFIC_EXPERT.get("any"),
+             peak_source=r["peak_source"] + " copy bandwidth (kernel timed inside a long step)")
+    return r
+
+
+def reference_triton(wl, gpu_index, timeout_s=900):
+    """The reference's own Triton forward on this GPU: its unmodified benchmark script (median of 100 wall-clock
+    forward + synchronize after 3 warm-ups) from the copy under baseline/_ref, in a subprocess, same model / views /
+    prompt length / chunk.  Returns {"p50_ms", "runs", "clocks"} or {"unavailable": why}."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.exists(os.path.join(ref_dir, "benchmark.py")):
+        return {"unavailable": "no copy of the reference under baseline/_ref on this machine"}
+    if wl.get("batch", 1) > 1 or wl.get("stages"):
+        return {"unavailable": "the reference has no batch dimension and no stage subset"}
+    cmd = [sys.executable, "benchmark.py", "--model_version", wl["model"], "--num_views", str(wl["num_views"]),
+           "--chunk_size", str(wl["chunk"]), "--prompt_len", str(wl["prompt_len"])]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES=os.environ.get("CUDA_VISIBLE_DEVICES", str(gpu_index)))
+    sampler = ClockSampler(gpu_index)
+    sampler.start()
+    t0 = time.time()
+    try:
+        res = subprocess.run(cmd, cwd=ref_dir, env=env, capture_output=True, text=True, timeout=timeout_s)
+    except subprocess.TimeoutExpired:
+        sampler.stop()
+        return {"unavailable": "the reference's benchmark script did not finish within %d s" % timeout_s}
+    clocks = sampler.stop()
+    import re
+    m = re.search(r"runs (\d+) median time per inference: ([0-9.]+) ms", res.stdout)
+    if res.returncode != 0 or not m:
+        tail = (res.stderr or res.stdout).strip().splitlines()[-1:] or [""]
+        return {"unavailable": "the reference's benchmark script failed (did not compile or run): %s" % tail[0][:200]}
+    return {"p50_ms": float(m.group(2)), "runs": int(m.group(1)), "clocks": clocks, "wall_s": round(time.time() - t0, 1),
+            "method": "reference benchmark.py: median of wall-clock forward + synchronize, 3 warm-ups, CUDA-graph replay"}
+
+
+def throughput_cfg5(device, local, flags, dist, world, steps=8):
+    """Throughput configuration in the same run: Pi0, 2 views, 20 prompt tokens, 32 observations per forward on each
+    GPU (device-resident inputs, CUDA events, max over ranks)."""
+    from pi0_infer import Pi0Inference
+    wl = dict(WORKLOADS["cfg5"])
+    ck = fast_checkpoint("pi0", wl["prompt_len"], wl["seed"], device)
+    infer = Pi0Inference(ck, wl["num_views"], wl["chunk"], device=local, flags=flags, batch=wl["batch"])
+    del ck
+    images, state, noise = inputs(wl, device)
+    for _ in range(3):
+        infer.forward(images, state, noise)
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        infer.forward(images, state, noise)
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = max_over_ranks(dist, device, [e0.elapsed_time(e1)])[0]
+    ok = infer._engine.status_word() == 0
+    del infer
+    torch.cuda.empty_cache()
+    return {"value": round(wl["batch"] * world * steps / (ms * 1e-3), 2), "unit": "obs/s", "n_gpus": world, "batch_per_gpu": wl["batch"],
+            "steps": steps, "ms_per_step": round(ms / steps, 3), "status_clean": ok,
+            "config": {k: wl[k] for k in ("model", "num_views", "prompt_len", "chunk")}, "clocks": clocks}
+
+
 def use_all_host_threads():
     """The CPU legs use every core this process may run on: torchrun exports OMP_NUM_THREADS=1 to its workers,
     which would otherwise leave the oracle on one thread."""
@@ -330,11 +426,12 @@ def oracle_forward_fn(wl, ck):
 def cpu_baseline(wl, ck, budget_s=25.0):
     """The fp32 oracle on the host cores: one full forward of the same workload (a bounded sample of 1 step)."""
     fn = oracle_forward_fn(wl, ck)
+    fn()                                   # warm-up: thread pool, allocator, page faults of the fp32 weight copies
     t0 = time.time()
     fn()
     dt = time.time() - t0
     return {"value": round(1.0 / dt, 5), "unit": "obs/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": "1 full forward of the workload (no warm-up), %.1f s" % dt}
+            "sample": "1 full forward of the workload after 1 warm-up forward, %.1f s" % dt}
 
 
 def run_reference(args, wl, rank, world):
@@ -344,7 +441,7 @@ def run_reference(args, wl, rank, world):
     ck = fast_checkpoint(wl["model"], wl["prompt_len"], wl["seed"], device)
     fn = oracle_forward_fn(wl, ck)
     del ck
-    warm = min(args.warmup, 1)
+    warm = args.warmup
     for _ in range(warm):
         fn()
     times, t_start = [], time.time()
@@ -450,6 +547,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-reference-triton", action="store_true", help="skip timing the reference's Triton forward (1-GPU runs only)")
+    ap.add_argument("--no-cfg5", action="store_true", help="skip the throughput configuration (32 observations per forward and GPU)")
     ap.add_argument("--batch", type=int, default=0, help="override the observations per forward of a workload (throughput mode)")
     ap.add_argument("--mode", default="replicas", choices=["replicas", "latency"],
                     help="replicas: every rank runs whole forwards (default); latency: one observation, one SigLIP tower "
@@ -496,6 +595,10 @@ def main():
             raise SystemExit("--mode latency needs torchrun with at least num_views ranks")
         run_latency_mode(args, wl, rank, world, local, device, dist)
         return
+
+    ref_triton = None
+    if world == 1 and not args.no_reference_triton:
+        ref_triton = reference_triton(wl, local)       # before this process holds GPU memory, outside every timed region
 
     if wl["model"] == "pi0":
         from pi0_infer import Pi0Inference
@@ -587,9 +690,18 @@ def main():
 
     total_ms, e2e_ms = max_over_ranks(dist, device, [total_ms, e2e_s * 1e3])
     stage_ms = infer._engine.time_stages()
+    obs = wl.get("batch", 1)          # observations per step and GPU
+    expert_roof = expert_stage_roofline(wl, infer, noise) if obs == 1 else None
+    single = obs == 1 and not wl.get("stages")
+    if not single or args.no_cfg5:
+        cfg5 = None
+    else:
+        if rank != 0:
+            del infer
+            torch.cuda.empty_cache()
+        cfg5 = throughput_cfg5(device, local, args.flags, dist, world)
 
     if rank == 0:
-        obs = wl.get("batch", 1)          # observations per step and GPU
         h2d = sum(x.numel() * 2 for x in host_args)
         d2h = obs * wl["chunk"] * 32 * 2
         line = {"metric": "observations_per_s", "value": round(obs * world * args.steps / (total_ms * 1e-3), 3), "unit": "obs/s",
@@ -609,14 +721,24 @@ def main():
         del infer
         torch.cuda.empty_cache()
         if wl.get("stages") == 4:
-            # the stage is a chain of ~930 launches, so the bound is stated for the stage as a whole: its
-            # algorithmic weight + K/V stream against the HBM copy peak (no single kernel dominates)
             line["config"]["stages"] = "action expert only (stage mask 4), K/V cache prefilled by one forward"
-            line["roofline"] = dict(decoder_stream(wl, total_ms / args.steps), kernel="action-expert stage, 10 Euler steps", traffic=None)
+        if expert_roof is not None:
+            # the expert stage owns most of a single-observation forward: it is the dominant "kernel" of the workload
+            line["roofline"] = expert_roof
+            line["roofline"]["share_of_forward"] = round(stage_ms[2] / max(sum(stage_ms), 1e-9), 3)
             line["decoder_stream"] = None
+            if not wl.get("stages"):
+                line["roofline_prefix"] = dominant_kernel_roofline(wl, device)
+                line["roofline_prefix"]["traffic"] = NCU_TRAFFIC_GEGLU.get(args.workload)
         else:
             line["roofline"] = dominant_kernel_roofline(wl, device)
-            line["roofline"]["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload)
+            line["roofline"]["traffic"] = NCU_TRAFFIC_GEGLU.get(args.workload)
+        if ref_triton is not None:
+            line["reference_triton"] = ref_triton
+            if "p50_ms" in ref_triton:
+                line["speedup_vs_triton"] = round(ref_triton["p50_ms"] / percentile(lat, 0.5), 3)
+        if cfg5 is not None:
+            line["throughput_cfg5"] = cfg5
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(wl, ck)
         print(json.dumps(line), flush=True)

@@ -63,3 +63,37 @@ def test_pi05_batch_shared_prompt():
         err = (out[b].float() - want).abs()
         print("observation %d: max-abs %.3e mean-abs %.3e" % (b, err.max().item(), err.mean().item()))
         assert err.max().item() <= 2e-2 and err.mean().item() <= 3e-3
+
+
+def test_throughput_configuration_full_depth():
+    """Throughput mode at its real shape: 32 observations per forward, 2 views, 20 prompt tokens, chunk 50, full
+    depth and 10 Euler steps (17 024 prefix tokens per call).  This is the only shape that drives the paired-tile
+    multi-wave GEMMs, the grouped tcgen05 attention over 32 groups and the batched SigLIP attention at depth.
+    Observations 0, 13 and 31 are checked against the per-observation oracle."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from pi0_infer import Pi0Inference
+    torch.backends.cuda.matmul.allow_tf32 = False
+    d = torch.device("cuda")
+    B, nv = 32, 2
+    ck = synth.make_checkpoint("pi0", seed=0, prompt_ids=synth.prompt_ids(20, 0))
+    ins = [synth.make_inputs(nv, 50, 100 + s) for s in range(B)]
+    images = torch.stack([i[0] for i in ins])
+    state = torch.stack([i[1] for i in ins])
+    noise = torch.stack([i[2] for i in ins])
+    infer = Pi0Inference(ck, nv, 50, batch=B)
+    out = infer.forward(images, state, noise).clone()
+    torch.cuda.synchronize()
+    assert tuple(out.shape) == (B, 50, 32)
+    assert infer._engine.status_word() == 0
+    assert torch.isfinite(out.float()).all()
+    del infer
+    w = {k: v.to(d).float() for k, v in ck.items()}
+    for b in (0, 13, 31):
+        vx = O.vision_encoder(w, images[b].to(d).float())
+        enc = torch.cat([O.project_vision(w, vx), w["language_embeds"]], 0)
+        K, V = O.prefix_encoder(w, enc)
+        want = O.pi0_decoder(w, K, V, state[b].to(d).float(), noise[b].to(d).float())
+        err = (out[b].float() - want).abs()
+        print("observation %d: max-abs %.3e mean-abs %.3e" % (b, err.max().item(), err.mean().item()))
+        assert err.max().item() <= 2e-2 and err.mean().item() <= 3e-3
