@@ -191,7 +191,10 @@ __device__ __forceinline__ void a_release(Ctx& c, unsigned int g) {
   if (c.lane == 0) mbar_arrive(c.a_empty + 8 * (g & 3u));
 }
 
-// Grid-wide barrier of the MMA warps of all CTAs.  Returns false after a timeout / abort.
+// Grid-wide barrier of the MMA warps of all CTAs.  Thread 0 arrives on the global counter; the activation warp is the
+// CTA's only poller of that counter (one poller per CTA keeps the L2 slice that holds it responsive): it publishes the
+// number of completed barriers in shared memory and at once issues the next phase's loads.  Returns false after a
+// timeout / abort.
 __device__ __forceinline__ bool grid_barrier(Ctx& c, int trace_slot) {
   cbar();
   if (c.tid == 0) {
@@ -200,13 +203,10 @@ __device__ __forceinline__ bool grid_barrier(Ctx& c, int trace_slot) {
     ++c.bar_epoch;
     __threadfence();
     asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.bar_ctr) : "memory");
-    const unsigned int target = c.bar_epoch * (unsigned int)p.G;
     const uint64_t t0 = globaltimer_ns();
-    unsigned int v, spins = 0;
-    for (;;) {
-      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.bar_ctr) : "memory");
-      if (v >= target) break;
-      if ((++spins & 255u) == 0) {
+    unsigned int spins = 0;
+    while (*c.go_count < (int)c.bar_epoch) {
+      if ((++spins & 1023u) == 0) {
         if (poll_abort(c)) break;
         if (globaltimer_ns() - t0 > VLA_WAIT_LIMIT_NS) {
           raise_timeout(c);
@@ -215,7 +215,6 @@ __device__ __forceinline__ bool grid_barrier(Ctx& c, int trace_slot) {
       }
     }
     __threadfence();
-    *c.go_count = (int)c.bar_epoch;    // the activation warp may now fetch what the other CTAs wrote
     if (p.trace && c.cta == 0) p.trace[2 * trace_slot + 1] = globaltimer_ns();
   } else {
     ++c.bar_epoch;
@@ -974,20 +973,26 @@ __device__ __forceinline__ void activation_producer_loop(Ctx& c) {
   const Params& p = *c.p;
   const uint64_t pol = policy_evict_last();
   unsigned int g = 0, att_n = 0;
-  int phase = 0;
+  int phase = -1;
   bool ok = true;
-  auto wait_go = [&](int needed) {
-    if (!ok) return;
+  // Start of the next phase: wait until the grid barrier in front of it has completed (every CTA has arrived), tell the
+  // MMA warps, and order the copies that follow behind the other CTAs' writes.
+  auto begin_phase = [&]() {
+    ++phase;
+    if (!ok || phase == 0) return;
+    const unsigned int target = (unsigned int)phase * (unsigned int)p.G;
     const uint64_t t0 = globaltimer_ns();
-    unsigned int spins = 0;
-    while (*c.go_count < needed) {
-      __nanosleep(32);   // a busy loop here would take issue slots from the MMA warps on this scheduler
+    unsigned int spins = 0, v;
+    for (;;) {
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.bar_ctr) : "memory");
+      if (v >= target) break;
       if ((++spins & 63u) == 0) {
         if (poll_abort(c)) { ok = false; return; }
         if (globaltimer_ns() - t0 > VLA_WAIT_LIMIT_NS) { raise_timeout(c); ok = false; return; }
       }
     }
     __threadfence();
+    *c.go_count = phase;
     fence_proxy_async_all();   // the rows were written through the generic proxy, the copies below read through the async one
   };
   auto stages = [&](const CUtensorMap* tm, int n_stages, int row0, int box_rows) {
@@ -1006,17 +1011,16 @@ __device__ __forceinline__ void activation_producer_loop(Ctx& c) {
   const bool owner = c.cta < N_OWNERS;
   const int n_items = p.att_nrb * p.att_ks;
   for (int step = 0; step < p.nsteps && ok; ++step) {
-    ++phase;                                        // action in-projection: loads its own rows
+    begin_phase();                                  // action in-projection: the MMA threads load its 50 x 32 tile themselves
     if (!p.pi05) {                                  // action MLP
-      if (owner) { wait_go(phase); stages(&p.tm_act, 4, 0, p.C); }
-      ++phase;
+      begin_phase();
+      if (owner) stages(&p.tm_act, 4, 0, p.C);
     }
     for (int l = 0; l < p.nl && ok; ++l) {
-      if (nq > 0) { wait_go(phase); stages(&p.tm_xb, 4, 0, p.S); }
-      ++phase;
-      if (c.cta < n_items) {                        // attention: K, V and Q tiles of this CTA's work item
-        wait_go(phase);
-        if (!ok) break;
+      begin_phase();                                // QKV
+      if (nq > 0) stages(&p.tm_xb, 4, 0, p.S);
+      begin_phase();                                // attention: K, V and Q tiles of this CTA's work item
+      if (c.cta < n_items && ok) {
         // the four stages of the QKV phase have been handed back by every warp before the barrier just passed
         const int rb = c.cta / p.att_ks, sp = c.cta - rb * p.att_ks;
         const int row_k = l * p.T + sp * p.att_kps;
@@ -1030,18 +1034,18 @@ __device__ __forceinline__ void activation_producer_loop(Ctx& c) {
         }
         ++att_n;
       }
-      ++phase;
-      ++phase;                                      // merge: reads global memory directly
-      if (owner) { wait_go(phase); stages(&p.tm_attn, 8, 0, p.S); }
-      ++phase;
-      if (owner) { wait_go(phase); stages(&p.tm_xb, 4, 0, p.S); }
-      ++phase;
-      if (owner) { wait_go(phase); stages(&p.tm_hidden, 16, 0, p.S); }
-      ++phase;
+      begin_phase();                                // merge: reads global memory directly
+      begin_phase();                                // attention-out projection
+      if (owner) stages(&p.tm_attn, 8, 0, p.S);
+      begin_phase();                                // GeGLU
+      if (owner) stages(&p.tm_xb, 4, 0, p.S);
+      begin_phase();                                // down projection
+      if (owner) stages(&p.tm_hidden, 16, 0, p.S);
     }
-    if (c.cta < 4) { wait_go(phase); stages(&p.tm_xb, 4, p.pi05 ? 0 : 1, p.S); }
-    ++phase;
+    begin_phase();                                  // out-projection + Euler update
+    if (c.cta < 4) stages(&p.tm_xb, 4, p.pi05 ? 0 : 1, p.S);
   }
+  if (ok) begin_phase();                            // the barrier behind the last phase: release the MMA warps
   if (!ok) {
     // bounded wait for copies still in flight
     for (unsigned int i = (g > 4 ? g - 4 : 0); i < g; ++i)
