@@ -53,7 +53,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # 788 tokens, and the persistent action-expert kernel (captured at reduced depth, scaled to 18 layers x 10 steps by
 # the layer-steps processed: its traffic is the weight stream, which grows in proportion).
 NCU_TRAFFIC_GEGLU = {"cfg2": 144519168}
-NCU_TRAFFIC_EXPERT = {}
+NCU_TRAFFIC_EXPERT = {"any": int(351.9e6 * 18)}
 
 
 def peaks():
@@ -64,14 +64,29 @@ def peaks():
     return dict(FALLBACK_PEAKS), "fallback"
 
 
+DEPTH = {"vit": 27, "layers": 18, "steps": 10}      # reduced only by the profiling options --vit-layers / --layers / --euler-steps
+
+
+def depth_kw():
+    """Keyword arguments of the inference classes for a reduced depth (nothing when the depth is the model's)."""
+    kw = {}
+    if DEPTH["vit"] != 27:
+        kw["n_vit_layers"] = DEPTH["vit"]
+    if DEPTH["layers"] != 18:
+        kw["n_layers"] = DEPTH["layers"]
+    if DEPTH["steps"] != 10:
+        kw["n_steps"] = DEPTH["steps"]
+    return kw
+
+
 def fast_checkpoint(model, prompt_len, seed, device):
     """Random bf16 checkpoint of the full-depth shapes, drawn on `device` (timing only: values follow the
     same N(0, 0.02) / unit-LayerNorm recipe as the parity tests but from the device generator)."""
     from oracle import synth
     shapes = {}
-    shapes.update(synth.vision_shapes(27))
-    shapes.update(synth.encoder_shapes(18))
-    shapes.update(synth.pi0_decoder_shapes(18) if model == "pi0" else synth.pi05_decoder_shapes(18))
+    shapes.update(synth.vision_shapes(DEPTH["vit"]))
+    shapes.update(synth.encoder_shapes(DEPTH["layers"]))
+    shapes.update(synth.pi0_decoder_shapes(DEPTH["layers"]) if model == "pi0" else synth.pi05_decoder_shapes(DEPTH["layers"]))
     g = torch.Generator(device=device).manual_seed(seed)
     ck = {}
     for k, shp in shapes.items():
@@ -560,6 +575,9 @@ def main():
                          "stream); expert_attention = suffix attention of the action expert on the tcgen05 kernel; siglip_attention = "
                          "attention of one SigLIP layer on the tcgen05 kernel; preprocess = camera "
                          "frames -> model input (resize, pad, normalise) on the device against the host code")
+    ap.add_argument("--vit-layers", type=int, default=27, help="profiling only: SigLIP layers (a reduced-depth model keeps an ncu capture small)")
+    ap.add_argument("--layers", type=int, default=18, help="profiling only: prefix / expert layers")
+    ap.add_argument("--euler-steps", type=int, default=10, help="profiling only: Euler steps")
     ap.add_argument("--profile-forward", action="store_true",
                     help="run two forwards and bracket the second with cudaProfilerStart/Stop (for ncu "
                          "--profile-from-start off); prints no benchmark line")
@@ -567,6 +585,9 @@ def main():
     wl = dict(WORKLOADS[args.workload])
     if args.batch > 0:
         wl["batch"] = args.batch
+    DEPTH.update(vit=args.vit_layers, layers=args.layers, steps=args.euler_steps)
+    if depth_kw() and not args.profile_forward:
+        raise SystemExit("a reduced depth is for --profile-forward only: a benchmark line is always the full model")
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -597,13 +618,13 @@ def main():
         return
 
     ref_triton = None
-    if world == 1 and not args.no_reference_triton:
+    if world == 1 and not args.no_reference_triton and not args.profile_forward:
         ref_triton = reference_triton(wl, local)       # before this process holds GPU memory, outside every timed region
 
     if wl["model"] == "pi0":
         from pi0_infer import Pi0Inference
         ck = fast_checkpoint("pi0", wl["prompt_len"], wl["seed"], device)
-        infer = Pi0Inference(ck, wl["num_views"], wl["chunk"], device=local, flags=args.flags, batch=wl.get("batch", 1))
+        infer = Pi0Inference(ck, wl["num_views"], wl["chunk"], device=local, flags=args.flags, batch=wl.get("batch", 1), **depth_kw())
         images, state, noise = inputs(wl, device)
         step = lambda: infer.forward(images, state, noise)
         host_args = [t.cpu().pin_memory() for t in (images, state, noise)]
@@ -627,7 +648,7 @@ def main():
         from pi05_infer import Pi05Inference
         ck = fast_checkpoint("pi05", wl["prompt_len"], wl["seed"], device)
         infer = Pi05Inference(ck, wl["num_views"], wl["chunk"], discrete_state_input=False, device=local, flags=args.flags,
-                              batch=wl.get("batch", 1))
+                              batch=wl.get("batch", 1), **depth_kw())
         images, state, noise = inputs(wl, device)
         step = lambda: infer.forward(images, noise)
         host_args = [t.cpu().pin_memory() for t in (images, noise)]
