@@ -75,6 +75,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tm, uint32
       ::"r"(dst), "l"(tm), "r"(bar), "r"(c0), "r"(c1), "l"(policy)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tm, uint32_t bar, int c0, int c1, int c2,
+                                            uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(dst), "l"(tm), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
+      : "memory");
+}
 // shared -> global tile store / fp32 reduce-add through TMA (bulk async-group completion)
 __device__ __forceinline__ void tma_store_2d(const void* tm, uint32_t src, int c0, int c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"

@@ -36,6 +36,7 @@ constexpr int A_BYTES = N_ASTAGE * STAGE_BYTES;   // 114688: activation stages /
 constexpr int SCR_BYTES = 8192;                   // GEMM: K-half exchange; attention: probabilities and row statistics
 constexpr int RING_OFF = A_BYTES + SCR_BYTES;
 constexpr int PERSIST_OFF = RING_OFF + NSLOT * CHUNK_BYTES;
+constexpr int MAX_SEQ = 500;              // weight chunks per Euler step and CTA (the order list in shared memory)
 constexpr int PERSIST_BYTES = 10240;          // barriers, per-token scales, this CTA's stream slice, rotary table of its QKV tiles
 constexpr int SMEM_BYTES = PERSIST_OFF + PERSIST_BYTES + 1024;   // + slack to align the base to 1024 B
 constexpr float SSQ_FIX = 16777216.0f;   // sums of squares travel as 40.24 fixed point: integer adds are order independent
@@ -47,12 +48,13 @@ constexpr int ATT_V_OFF = ATT_MAX_KEYS * 512;     // V tiles behind the K tiles
 constexpr int ATT_Q_OFF = 2 * ATT_MAX_KEYS * 512; // Q tiles (16 KB) fill the rest of the activation region
 
 struct Params {
-  CUtensorMap tm_xb;      // bf16 mirror of the stream [S, 1024], box 64 x S
-  CUtensorMap tm_act;     // Pi0 action MLP input [C, 1024], box 64 x C
+  // all maps are 3-D (64 elements, rows, 64-wide blocks of the row), 128-byte swizzle: one copy brings [block][row][128 B]
+  CUtensorMap tm_xb;      // bf16 mirror of the stream [S, 1024], box 64 x MAX_ROWS x 4
+  CUtensorMap tm_act;     // Pi0 action MLP input [C, 1024], same box
   CUtensorMap tm_attn;    // attention output [S, 2048], box 64 x S
   CUtensorMap tm_hidden;  // MLP hidden [S, 4096], box 64 x S
-  CUtensorMap tm_q;       // queries as [S * 8, 256], box 64 x 32
-  CUtensorMap tm_k;       // key cache [layers * T, 256], box 64 x att_kps
+  CUtensorMap tm_q;       // queries as [S * 8, 256], box 64 x 32 x 4
+  CUtensorMap tm_k;       // key cache [layers * T, 256], box 64 x att_kps x 4
   CUtensorMap tm_v;       // value cache, same
   int pi05, S, C, P, T, nl, nsteps, G;
   int att_nrb, att_ks, att_kps;   // row blocks, key splits, keys per split (multiple of 16, <= ATT_MAX_KEYS)
@@ -160,17 +162,41 @@ __device__ __forceinline__ void raise_timeout(Ctx& c) {
   atomicOr(c.p->bar_ctr + 1, 1u);
   atomicOr(c.p->status, VLA_ST_WAIT_TIMEOUT);
 }
-// bounded mbarrier wait; false = gave up (status word raised) or another CTA / role gave up
-__device__ __forceinline__ bool wait_bar(Ctx& c, uint32_t bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
+// bounded mbarrier wait; false = gave up (status word raised) or another CTA / role gave up.  (Kept inline: as separate
+// functions the waiting loops cost 10 % of the kernel's time.)
+__device__ __forceinline__ bool wait_bar_slow(uint32_t bar, uint32_t parity, volatile int* s_abort, unsigned int* bar_ctr, int* status) {
   const uint64_t t0 = globaltimer_ns();
   for (;;) {
     for (int i = 0; i < 128; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (poll_abort(c)) return false;
+    if (*s_abort) return false;
+    if (*reinterpret_cast<volatile unsigned int*>(bar_ctr + 1)) { *s_abort = 1; return false; }
     if (globaltimer_ns() - t0 > VLA_WAIT_LIMIT_NS) {
-      raise_timeout(c);
+      *s_abort = 1;
+      atomicOr(bar_ctr + 1, 1u);
+      atomicOr(status, VLA_ST_WAIT_TIMEOUT);
       return false;
+    }
+  }
+}
+__device__ __forceinline__ bool wait_bar(Ctx& c, uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return wait_bar_slow(bar, parity, c.s_abort, c.p->bar_ctr, c.p->status);
+}
+// bounded wait of MMA thread 0 for the count of completed grid barriers that the activation warp publishes
+__device__ __forceinline__ void go_wait_slow(volatile int* go, int need, volatile int* s_abort, unsigned int* bar_ctr, int* status) {
+  const uint64_t t0 = globaltimer_ns();
+  unsigned int spins = 0;
+  while (*go < need) {
+    if ((++spins & 1023u) == 0) {
+      if (*s_abort) return;
+      if (*reinterpret_cast<volatile unsigned int*>(bar_ctr + 1)) { *s_abort = 1; return; }
+      if (globaltimer_ns() - t0 > VLA_WAIT_LIMIT_NS) {
+        *s_abort = 1;
+        atomicOr(bar_ctr + 1, 1u);
+        atomicOr(status, VLA_ST_WAIT_TIMEOUT);
+        return;
+      }
     }
   }
 }
@@ -194,30 +220,18 @@ __device__ __forceinline__ void a_release(Ctx& c, unsigned int g) {
 // Grid-wide barrier of the MMA warps of all CTAs.  Thread 0 arrives on the global counter; the activation warp is the
 // CTA's only poller of that counter (one poller per CTA keeps the L2 slice that holds it responsive): it publishes the
 // number of completed barriers in shared memory and at once issues the next phase's loads.  Returns false after a
-// timeout / abort.
+// timeout / abort (the same value in every MMA thread).
 __device__ __forceinline__ bool grid_barrier(Ctx& c, int trace_slot) {
   cbar();
+  ++c.bar_epoch;
   if (c.tid == 0) {
     const Params& p = *c.p;
     if (p.trace && c.cta == 0) p.trace[2 * trace_slot] = globaltimer_ns();
-    ++c.bar_epoch;
     __threadfence();
     asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.bar_ctr) : "memory");
-    const uint64_t t0 = globaltimer_ns();
-    unsigned int spins = 0;
-    while (*c.go_count < (int)c.bar_epoch) {
-      if ((++spins & 1023u) == 0) {
-        if (poll_abort(c)) break;
-        if (globaltimer_ns() - t0 > VLA_WAIT_LIMIT_NS) {
-          raise_timeout(c);
-          break;
-        }
-      }
-    }
-    __threadfence();
+    if (*c.go_count < (int)c.bar_epoch) go_wait_slow(c.go_count, (int)c.bar_epoch, c.s_abort, p.bar_ctr, p.status);
+    __threadfence_block();   // the loader's acquire at GPU scope, its store of the count, this read and the barrier below form the chain
     if (p.trace && c.cta == 0) p.trace[2 * trace_slot + 1] = globaltimer_ns();
-  } else {
-    ++c.bar_epoch;
   }
   cbar();
   return *c.s_abort == 0;
@@ -250,7 +264,7 @@ __device__ __forceinline__ void ssq_add(const Ctx& c, int token, float sq) {
 // instead of after it.  chunk_g0 = index of the first chunk of the pass.
 template <int NT, bool QUARTERS = false>
 __device__ __forceinline__ void mma_resident(Ctx& c, const uint32_t* sl, int rows, unsigned int a_g0, float (&acc)[NT][4], bool* ok,
-                                             unsigned int chunk_g0 = 0) {
+                                             unsigned int chunk_g0 = 0, int nt = NT) {
   static_assert(!QUARTERS || NT == 4, "the quarter layout holds four tiles per chunk");
   const int mi = c.warp & 3, kh = c.warp >> 2;
   float acc2[4] = {0.f, 0.f, 0.f, 0.f};   // a single tile alternates two accumulators to break the dependent chain
@@ -287,6 +301,7 @@ __device__ __forceinline__ void mma_resident(Ctx& c, const uint32_t* sl, int row
     }
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
+      if (t >= nt) break;                // fewer tiles than NT: the same in every thread
       const uint32_t baddr = QUARTERS ? qbase + (uint32_t)t * 4096 : sl[t] + (uint32_t)(2 * kb) * 512 + lane_off;
       const uint4 b0 = lds128(baddr);
       const uint4 b1 = lds128(baddr + 512);
@@ -524,9 +539,15 @@ __device__ __forceinline__ bool phase_action_mlp(Ctx& c) {
 
 // QKV projection with folded norm, rotary embedding and K/V-cache append (pi0_infer.py:777-810).
 // CTA c owns feature tiles c, c + G, c + 2G (< 320).
-template <int NQ>
-__device__ __forceinline__ bool qkv_tiles(Ctx& c, int step, int layer) {
+__device__ __forceinline__ int qkv_tile_count(int cta, int G) {
+  return (cta + 2 * G < 320) ? 3 : ((cta + G < 320) ? 2 : (cta < 320 ? 1 : 0));
+}
+__device__ __forceinline__ bool phase_qkv(Ctx& c, int step, int layer) {
+  constexpr int NQ = 3;
   const Params& p = *c.p;
+  const int nq = qkv_tile_count(c.cta, p.G);   // tiles of this CTA (<= NQ); one instantiation serves every count
+  if (nq == 0) return true;
+  XP_MARK(c, 0);
   bool ok = true;
   const int mi = c.warp & 3, kh = c.warp >> 2;
   // the few values the epilogue needs from global memory are requested before the MMAs
@@ -537,6 +558,7 @@ __device__ __forceinline__ bool qkv_tiles(Ctx& c, int step, int layer) {
     const float* bsrc = p.sw_qkv + ((size_t)step * p.nl + layer) * 2560;
 #pragma unroll
     for (int t = 0; t < NQ; ++t) {
+      if (t >= nq) break;
       const int n = 8 * (c.cta + t * p.G) + 2 * (c.lane & 3);
       bias[t][0] = bsrc[n];
       bias[t][1] = bsrc[n + 1];
@@ -545,15 +567,16 @@ __device__ __forceinline__ bool qkv_tiles(Ctx& c, int step, int layer) {
   const unsigned long long fv = fs_issue(c);
   uint32_t sl[NQ];
 #pragma unroll
-  for (int j = 0; j < NQ; ++j) sl[j] = acquire_chunk(c, c.chunk_g + j, &ok);
+  for (int j = 0; j < NQ; ++j) sl[j] = j < nq ? acquire_chunk(c, c.chunk_g + j, &ok) : 0u;
   XP_MARK(c, 1);
   float acc[NQ][4];
-  mma_resident<NQ>(c, sl, p.S, c.a_g, acc, &ok);
+  mma_resident<NQ>(c, sl, p.S, c.a_g, acc, &ok, 0, nq);
   XP_MARK(c, 2);
 #pragma unroll
-  for (int j = 0; j < NQ; ++j) release_chunk(c, c.chunk_g + j);
+  for (int j = 0; j < NQ; ++j)
+    if (j < nq) release_chunk(c, c.chunk_g + j);
   a_release4(c);
-  c.chunk_g += NQ;
+  c.chunk_g += nq;
   fs_finish(c, fv);
   reduce_khalves<NQ>(c, false, acc);   // the barrier inside also publishes fs
   XP_MARK(c, 3);
@@ -562,6 +585,7 @@ __device__ __forceinline__ bool qkv_tiles(Ctx& c, int step, int layer) {
     bf16* vc = p.vcache + (size_t)layer * p.T * 256;
 #pragma unroll
     for (int t = 0; t < NQ; ++t) {
+      if (t >= nq) break;
       const int n = 8 * (c.cta + t * p.G) + 2 * (c.lane & 3);
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -580,17 +604,6 @@ __device__ __forceinline__ bool qkv_tiles(Ctx& c, int step, int layer) {
   XP_MARK(c, 4);
   return ok;
 }
-__device__ __forceinline__ int qkv_tile_count(int cta, int G) {
-  return (cta + 2 * G < 320) ? 3 : ((cta + G < 320) ? 2 : (cta < 320 ? 1 : 0));
-}
-__device__ __forceinline__ bool phase_qkv(Ctx& c, int step, int layer) {
-  const int nq = qkv_tile_count(c.cta, c.p->G);
-  XP_MARK(c, 0);
-  if (nq == 3) return qkv_tiles<3>(c, step, layer);
-  if (nq == 2) return qkv_tiles<2>(c, step, layer);
-  if (nq == 1) return qkv_tiles<1>(c, step, layer);
-  return true;
-}
 
 // GeGLU: hidden[:, 32c..32c+31] = gelu(f * (xb @ Wg) + bg) * (f * (xb @ Wu) + bu), four (gate, up) tile pairs per CTA.
 __device__ __forceinline__ bool phase_geglu(Ctx& c, int step, int layer) {
@@ -599,21 +612,19 @@ __device__ __forceinline__ bool phase_geglu(Ctx& c, int step, int layer) {
   bool ok = true;
   XP_MARK(c, 60);
   const int mi = c.warp & 3, kh = c.warp >> 2;
-  float bg[4][2], bu[4][2];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) { bg[i][0] = bg[i][1] = bu[i][0] = bu[i][1] = 0.f; }
-  if (p.pi05 && kh == 0) {
-    const float* g = p.sw_gate + ((size_t)step * p.nl + layer) * 4096;
-    const float* u = p.sw_up + ((size_t)step * p.nl + layer) * 4096;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int n = 32 * c.cta + 8 * i + 2 * (c.lane & 3);
-      bg[i][0] = g[n]; bg[i][1] = g[n + 1]; bu[i][0] = u[n]; bu[i][1] = u[n + 1];
-    }
-  }
   const unsigned long long fv = fs_issue(c);
-#pragma unroll
+#pragma unroll 1
   for (int pass = 0; pass < 2; ++pass) {     // tiles (gate, up, gate, up) of pairs 2 pass, 2 pass + 1 share the A fragments
+    float bg[2][2] = {{0.f, 0.f}, {0.f, 0.f}}, bu[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+    if (p.pi05 && kh == 0) {
+      const float* g = p.sw_gate + ((size_t)step * p.nl + layer) * 4096;
+      const float* u = p.sw_up + ((size_t)step * p.nl + layer) * 4096;
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int n = 32 * c.cta + 8 * (2 * pass + q) + 2 * (c.lane & 3);
+        bg[q][0] = g[n]; bg[q][1] = g[n + 1]; bu[q][0] = u[n]; bu[q][1] = u[n + 1];
+      }
+    }
     float acc[4][4];
     mma_resident<4, true>(c, nullptr, p.S, c.a_g, acc, &ok, c.chunk_g);   // waits for and hands back its chunks quarter by quarter
     c.chunk_g += 4;
@@ -623,15 +634,14 @@ __device__ __forceinline__ bool phase_geglu(Ctx& c, int step, int layer) {
     if (kh == 0) {
 #pragma unroll
       for (int q = 0; q < 2; ++q) {
-        const int i = 2 * pass + q;
-        const int n = 32 * c.cta + 8 * i + 2 * (c.lane & 3);
+        const int n = 32 * c.cta + 8 * (2 * pass + q) + 2 * (c.lane & 3);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int r = 16 * mi + (c.lane >> 2) + 8 * h;
           if (r >= p.S) continue;
           const float f = c.fs[r];
-          const float h0 = gelu_tanh_f(f * acc[2 * q][2 * h] + bg[i][0]) * (f * acc[2 * q + 1][2 * h] + bu[i][0]);
-          const float h1 = gelu_tanh_f(f * acc[2 * q][2 * h + 1] + bg[i][1]) * (f * acc[2 * q + 1][2 * h + 1] + bu[i][1]);
+          const float h0 = gelu_tanh_f(f * acc[2 * q][2 * h] + bg[q][0]) * (f * acc[2 * q + 1][2 * h] + bu[q][0]);
+          const float h1 = gelu_tanh_f(f * acc[2 * q][2 * h + 1] + bg[q][1]) * (f * acc[2 * q + 1][2 * h + 1] + bu[q][1]);
           *reinterpret_cast<uint32_t*>(p.hidden + (size_t)r * 4096 + n) = pack_bf16x2(h0, h1);
         }
       }
@@ -930,31 +940,38 @@ __device__ __forceinline__ void phase_attention_merge(Ctx& c) {
 }
 
 // ---- weight stream (warp 8, one lane) ---------------------------------------------------------------------------------------
+// The CTA's chunks in the order its phases consume them (the same order in every Euler step), copied into the ring as
+// its slots are handed back.  (Requesting chunks into L2 ahead of the copy, cp.async.bulk.prefetch.L2, made the kernel
+// 2.5 % slower and is not done.)
 __device__ __forceinline__ void weight_producer_loop(Ctx& c) {
   const Params& p = *c.p;
   const uint4* base = p.wstream + (size_t)c.cta * p.chunks_per_cta * (CHUNK_BYTES / 16);
-  const uint64_t pol = policy_evict_first();
+  const uint64_t pol = policy_evict_first();    // a chunk is read once per Euler step
+  unsigned short* seq = reinterpret_cast<unsigned short*>(c.sptr + PERSIST_OFF + 9216);
+  int n = 0;
+  {
+    auto range = [&](int first, int count) {
+      for (int j = 0; j < count && n < MAX_SEQ; ++j) seq[n++] = (unsigned short)(first + j);
+    };
+    const int nq = qkv_tile_count(c.cta, p.G);
+    const bool owner = c.cta < N_OWNERS;
+    if (!p.pi05 && owner) range(p.misc_base, 1);
+    for (int l = 0; l < p.nl; ++l) {
+      range(l * CH_PER_LAYER, nq);
+      if (owner) range(l * CH_PER_LAYER + 3, CH_PER_LAYER - 3);   // attention-out, GeGLU quarters, down
+    }
+    if (c.cta < 4) range(p.misc_base + 1, 1);
+  }
+  const long long total = (long long)n * p.nsteps;
   unsigned int g = 0;
-  bool ok = true;
-  auto push = [&](int idx) {
-    if (!ok) return;
+  bool ok = n > 0;
+  for (long long pos = 0; pos < total && ok; ++pos) {
     const unsigned int s = g % NSLOT;
     if (g >= NSLOT) ok = wait_bar(c, c.w_empty + 8 * s, ((g / NSLOT) - 1) & 1u);
-    if (!ok) return;
+    if (!ok) break;
     mbar_expect_tx(c.w_full + 8 * s, CHUNK_BYTES);
-    bulk_g2s(c.sbase + RING_OFF + s * CHUNK_BYTES, base + (size_t)idx * (CHUNK_BYTES / 16), CHUNK_BYTES, c.w_full + 8 * s, pol);
+    bulk_g2s(c.sbase + RING_OFF + s * CHUNK_BYTES, base + (size_t)seq[pos % n] * (CHUNK_BYTES / 16), CHUNK_BYTES, c.w_full + 8 * s, pol);
     ++g;
-  };
-  const int nq = qkv_tile_count(c.cta, p.G);
-  const bool owner = c.cta < N_OWNERS;
-  for (int step = 0; step < p.nsteps && ok; ++step) {
-    if (!p.pi05 && owner) push(p.misc_base);
-    for (int l = 0; l < p.nl && ok; ++l) {
-      for (int j = 0; j < nq; ++j) push(l * CH_PER_LAYER + j);
-      if (owner)
-        for (int j = 3; j < CH_PER_LAYER; ++j) push(l * CH_PER_LAYER + j);
-    }
-    if (c.cta < 4) push(p.misc_base + 1);
   }
   if (!ok) {
     // give the copies still in flight time to land before the CTA can retire (bounded)
@@ -991,19 +1008,18 @@ __device__ __forceinline__ void activation_producer_loop(Ctx& c) {
         if (globaltimer_ns() - t0 > VLA_WAIT_LIMIT_NS) { raise_timeout(c); ok = false; return; }
       }
     }
-    __threadfence();
+    __threadfence_block();
     *c.go_count = phase;
     fence_proxy_async_all();   // the rows were written through the generic proxy, the copies below read through the async one
   };
-  auto stages = [&](const CUtensorMap* tm, int n_stages, int row0, int box_rows) {
+  // one stage = four 64-wide K blocks of MAX_ROWS rows from row0 on (rows past the tensor are filled with zeros), one copy
+  auto stages = [&](const CUtensorMap* tm, int n_stages, int row0) {
     for (int st = 0; st < n_stages && ok; ++st) {
       const unsigned int s = g & 3u;
       if (g >= 4) ok = wait_bar(c, c.a_empty + 8 * s, ((g >> 2) - 1) & 1u);
       if (!ok) return;
-      mbar_expect_tx(c.a_full + 8 * s, (uint32_t)(4 * box_rows * 128));
-#pragma unroll
-      for (int t = 0; t < 4; ++t)
-        tma_load_2d(c.sbase + s * STAGE_BYTES + t * TILE_BYTES, tm, c.a_full + 8 * s, st * 256 + t * 64, row0, pol);
+      mbar_expect_tx(c.a_full + 8 * s, STAGE_BYTES);
+      tma_load_3d(c.sbase + s * STAGE_BYTES, tm, c.a_full + 8 * s, 0, row0, st * 4, pol);
       ++g;
     }
   };
@@ -1014,11 +1030,11 @@ __device__ __forceinline__ void activation_producer_loop(Ctx& c) {
     begin_phase();                                  // action in-projection: the MMA threads load its 50 x 32 tile themselves
     if (!p.pi05) {                                  // action MLP
       begin_phase();
-      if (owner) stages(&p.tm_act, 4, 0, p.C);
+      if (owner) stages(&p.tm_act, 4, 0);
     }
     for (int l = 0; l < p.nl && ok; ++l) {
       begin_phase();                                // QKV
-      if (nq > 0) stages(&p.tm_xb, 4, 0, p.S);
+      if (nq > 0) stages(&p.tm_xb, 4, 0);
       begin_phase();                                // attention: K, V and Q tiles of this CTA's work item
       if (c.cta < n_items && ok) {
         // the four stages of the QKV phase have been handed back by every warp before the barrier just passed
@@ -1026,24 +1042,21 @@ __device__ __forceinline__ void activation_producer_loop(Ctx& c) {
         const int row_k = l * p.T + sp * p.att_kps;
         const uint32_t kv_tile = (uint32_t)p.att_kps * 128;
         mbar_expect_tx(c.att_full, 4 * 4096 + 8 * kv_tile);
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          tma_load_2d(c.sbase + t * kv_tile, &p.tm_k, c.att_full, 64 * t, row_k, pol);
-          tma_load_2d(c.sbase + ATT_V_OFF + t * kv_tile, &p.tm_v, c.att_full, 64 * t, row_k, pol);
-          tma_load_2d(c.sbase + ATT_Q_OFF + t * 4096, &p.tm_q, c.att_full, 64 * t, rb * ATT_ROWS, pol);
-        }
+        tma_load_3d(c.sbase, &p.tm_k, c.att_full, 0, row_k, 0, pol);               // the four 64-dim blocks in one copy each
+        tma_load_3d(c.sbase + ATT_V_OFF, &p.tm_v, c.att_full, 0, row_k, 0, pol);
+        tma_load_3d(c.sbase + ATT_Q_OFF, &p.tm_q, c.att_full, 0, rb * ATT_ROWS, 0, pol);
         ++att_n;
       }
       begin_phase();                                // merge: reads global memory directly
       begin_phase();                                // attention-out projection
-      if (owner) stages(&p.tm_attn, 8, 0, p.S);
+      if (owner) stages(&p.tm_attn, 8, 0);
       begin_phase();                                // GeGLU
-      if (owner) stages(&p.tm_xb, 4, 0, p.S);
+      if (owner) stages(&p.tm_xb, 4, 0);
       begin_phase();                                // down projection
-      if (owner) stages(&p.tm_hidden, 16, 0, p.S);
+      if (owner) stages(&p.tm_hidden, 16, 0);
     }
     begin_phase();                                  // out-projection + Euler update
-    if (c.cta < 4) stages(&p.tm_xb, 4, p.pi05 ? 0 : 1, p.S);
+    if (c.cta < 4) stages(&p.tm_xb, 4, p.pi05 ? 0 : 1);
   }
   if (ok) begin_phase();                            // the barrier behind the last phase: release the MMA warps
   if (!ok) {
@@ -1127,49 +1140,55 @@ __global__ void __launch_bounds__(THREADS, 1) expert_persistent_kernel(const __g
     if (c.lane == 0) activation_producer_loop(c);
     __syncwarp();
   } else {
-    bool ok = true;
-    int ph = 0;   // phase counter (trace slot)
+    bool ok = true;   // false once the kernel is being aborted
     if (!p.pi05 && c.cta < N_OWNERS && c.tid < 8) {   // state token features of this CTA (pi0_infer.py:1166-1171)
       const int n = 8 * c.cta + c.tid;
       float acc = p.b_state[n];
       for (int k = 0; k < 32; ++k) acc += __bfloat162float(p.state[k]) * __bfloat162float(p.w_state[(size_t)n * 64 + k]);
       c.sttok[c.tid] = acc;
     }
-    for (int step = 0; step < p.nsteps && ok; ++step) {
-      phase_in_proj(c, step);
-      ok = grid_barrier(c, ph++);
-      if (!p.pi05 && ok) {
-        ok = phase_action_mlp(c);
-        ok = grid_barrier(c, ph++) && ok;
+    // The kernel's schedule as one loop over phases, so that the code of every phase exists once (the kernel is larger
+    // than the instruction cache; every copy costs fetch time).  Per Euler step: in-projection, (Pi0) action MLP, per
+    // layer QKV, attention, merge, attention-out, GeGLU, down; then the out-projection.  A grid barrier follows every
+    // phase.  What a phase function returns (a wait of this warp gave up) is not used for control flow: the abort word,
+    // read behind a CTA barrier and so the same in every MMA thread, is.
+    enum { K_IN, K_MLP, K_QKV, K_ATT, K_MRG, K_O, K_GEGLU, K_DOWN, K_OUT };
+    const int head = p.pi05 ? 1 : 2;
+    const int per_step = head + 6 * p.nl + 1;
+#pragma unroll 1
+    for (int ph = 0; ph < p.nsteps * per_step && ok; ++ph) {
+      const int step = ph / per_step, r = ph - step * per_step;
+      int kind, l = 0;
+      if (r < head) kind = r == 0 ? K_IN : K_MLP;
+      else if (r == per_step - 1) kind = K_OUT;
+      else { l = (r - head) / 6; kind = K_QKV + (r - head) - 6 * l; }
+      const size_t sl = (size_t)step * p.nl + l;
+      c.fine = p.trace != nullptr && c.cta == 0 && step == 0 && l == 1 && kind >= K_QKV && kind <= K_DOWN;
+      switch (kind) {
+        case K_IN: phase_in_proj(c, step); break;
+        case K_MLP: phase_action_mlp(c); break;
+        case K_QKV: phase_qkv(c, step, l); break;
+        case K_ATT: phase_attention(c, l); break;
+        case K_MRG: phase_attention_merge(c); break;
+        case K_O:
+        case K_DOWN: {
+          const bool o = kind == K_O;
+          const float* gate = nullptr;
+          const float* next_scale = nullptr;
+          if (p.pi05) {
+            gate = (o ? p.style_attn : p.style_ffn) + sl * 3072 + 2048;
+            next_scale = o ? p.style_ffn + sl * 3072
+                           : ((l + 1 < p.nl) ? p.style_attn + (sl + 1) * 3072 : p.style_fin + (size_t)step * 3072);
+          }
+          phase_resid(c, o ? 2048 : 4096, gate, next_scale);
+          break;
+        }
+        case K_GEGLU: phase_geglu(c, step, l); break;
+        default: phase_out(c, step); break;
       }
-      for (int l = 0; l < p.nl && ok; ++l) {
-        c.fine = p.trace != nullptr && c.cta == 0 && step == 0 && l == 1;
-        ok = phase_qkv(c, step, l);
-        ok = grid_barrier(c, ph++) && ok;
-        if (!ok) break;
-        ok = phase_attention(c, l);
-        ok = grid_barrier(c, ph++) && ok;
-        if (!ok) break;
-        phase_attention_merge(c);
-        ok = grid_barrier(c, ph++);
-        if (!ok) break;
-        const size_t sl = (size_t)step * p.nl + l;
-        ok = phase_resid(c, 2048, p.pi05 ? p.style_attn + sl * 3072 + 2048 : nullptr, p.pi05 ? p.style_ffn + sl * 3072 : nullptr);
-        ok = grid_barrier(c, ph++) && ok;
-        if (!ok) break;
-        ok = phase_geglu(c, step, l);
-        ok = grid_barrier(c, ph++) && ok;
-        if (!ok) break;
-        const float* next_scale = nullptr;
-        if (p.pi05) next_scale = (l + 1 < p.nl) ? p.style_attn + (sl + 1) * 3072 : p.style_fin + (size_t)step * 3072;
-        ok = phase_resid(c, 4096, p.pi05 ? p.style_ffn + sl * 3072 + 2048 : nullptr, next_scale);
-        ok = grid_barrier(c, ph++) && ok;
-      }
-      c.fine = false;
-      if (!ok) break;
-      ok = phase_out(c, step);
-      ok = grid_barrier(c, ph++) && ok;
+      ok = grid_barrier(c, ph);
     }
+    c.fine = false;
     if (!ok) *c.s_abort = 1;
   }
   __syncthreads();

@@ -74,6 +74,29 @@ bool make_tmap(CUtensorMap* tm, const void* base, long long K, long long rows, l
   return true;
 }
 
+// The same operand as a 3-D map (64 elements, rows, K / 64 blocks): one copy of box 64 x box_rows x box_blocks lands as
+// [block][row][128 B], i.e. box_blocks consecutive 64-wide K blocks of the same rows (rows past the tensor read as zeros).
+bool make_tmap3(CUtensorMap* tm, const void* base, long long K, long long rows, long long ld, int box_rows, int box_blocks,
+                std::string* err) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) { *err = "cuTensorMapEncodeTiled entry point not found"; return false; }
+  cuuint64_t dims[3] = {64u, (cuuint64_t)rows, (cuuint64_t)(K / 64)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, 128u};
+  cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, (cuuint32_t)box_blocks};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[256];
+    snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled (3-D) failed (%d) K=%lld rows=%lld ld=%lld box_rows=%d base=%p", (int)r, K,
+             rows, ld, box_rows, base);
+    *err = buf;
+    return false;
+  }
+  return true;
+}
+
 // output tile map for TMA stores: [rows, cols] row-major with pitch ld (elements), box 32 x 32, no swizzle
 bool make_out_tmap(CUtensorMap* tm, const void* base, bool f32, long long cols, long long rows, long long ld, std::string* err) {
   EncodeTiledFn fn = get_encode_fn();
@@ -946,15 +969,15 @@ void plan_decoder_persistent(Plan& pl) {
   p.hidden = m->decoder_hidden; p.att_part = m->xp_part; p.att_stat = m->xp_stat;
   p.rope_cos = m->rope_cos; p.rope_sin = m->rope_sin;
   p.bar_ctr = m->xp_sync; p.status = m->d_status; p.trace = nullptr;
-  // activation operands come in by TMA: 64-wide K blocks of all rows, 128-byte swizzle
+  // activation operands come in by TMA: four 64-wide K blocks of MAX_ROWS rows per copy, 128-byte swizzle
   const bool maps_ok =
-      make_tmap(&p.tm_xb, m->decoder_xb, 1024, m->S, 1024, m->S, &pl.err) &&
-      make_tmap(&p.tm_act, m->decoder_act, 1024, m->C, 1024, m->C, &pl.err) &&
-      make_tmap(&p.tm_attn, m->decoder_attn, 2048, m->S, 2048, m->S, &pl.err) &&
-      make_tmap(&p.tm_hidden, m->decoder_hidden, 4096, m->S, 4096, m->S, &pl.err) &&
-      make_tmap(&p.tm_q, m->decoder_q, 256, m->S * 8, 256, xp::ATT_ROWS, &pl.err) &&
-      make_tmap(&p.tm_k, m->kcache, 256, (long long)m->nl * m->T, 256, p.att_kps, &pl.err) &&
-      make_tmap(&p.tm_v, m->vcache, 256, (long long)m->nl * m->T, 256, p.att_kps, &pl.err);
+      make_tmap3(&p.tm_xb, m->decoder_xb, 1024, m->S, 1024, xp::MAX_ROWS, 4, &pl.err) &&
+      make_tmap3(&p.tm_act, m->decoder_act, 1024, m->C, 1024, xp::MAX_ROWS, 4, &pl.err) &&
+      make_tmap3(&p.tm_attn, m->decoder_attn, 2048, m->S, 2048, xp::MAX_ROWS, 4, &pl.err) &&
+      make_tmap3(&p.tm_hidden, m->decoder_hidden, 4096, m->S, 4096, xp::MAX_ROWS, 4, &pl.err) &&
+      make_tmap3(&p.tm_q, m->decoder_q, 256, m->S * 8, 256, xp::ATT_ROWS, 4, &pl.err) &&
+      make_tmap3(&p.tm_k, m->kcache, 256, (long long)m->nl * m->T, 256, p.att_kps, 4, &pl.err) &&
+      make_tmap3(&p.tm_v, m->vcache, 256, (long long)m->nl * m->T, 256, p.att_kps, 4, &pl.err);
   if (!maps_ok) { pl.ok = false; return; }
   pl.kernel([m](cudaStream_t st) { return launch_expert_persistent(m, st, nullptr); });
 }
