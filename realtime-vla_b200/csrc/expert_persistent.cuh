@@ -142,12 +142,16 @@ struct Ctx {
   int cta, warp, lane, tid;
   int valid_len, pos_base;
   bool fine;
+  int nmark;
 };
 
-// development timeline inside phases: CTA 0, thread 0, Euler step 0, layer 1 only -> trace[2560 + id]
+// development timeline inside phases (CTA 0, Euler step 0, layer 1 only): append-only logs of (id << 48 | clock64),
+// MMA thread 0 at trace[2560..], the activation warp at [3400..], the weight warp at [3700..]
 #ifdef XP_FINE_TRACE
-#define XP_MARK(c, id) do { if ((c).fine && (c).tid == 0) (c).p->trace[2560 + (id)] = (unsigned long long)clock64(); } while (0)
+#define XP_LOG(c, base, cap, id) do { if ((c).fine && (c).nmark < (cap)) { (c).p->trace[(base) + (c).nmark] = ((unsigned long long)(id) << 48) | ((unsigned long long)clock64() & 0xffffffffffffull); ++(c).nmark; } } while (0)
+#define XP_MARK(c, id) do { if ((c).tid == 0) XP_LOG(c, 2560, 800, id); } while (0)
 #else
+#define XP_LOG(c, base, cap, id) do {} while (0)
 #define XP_MARK(c, id) do {} while (0)
 #endif
 
@@ -227,8 +231,10 @@ __device__ __forceinline__ bool grid_barrier(Ctx& c, int trace_slot) {
   if (c.tid == 0) {
     const Params& p = *c.p;
     if (p.trace && c.cta == 0) p.trace[2 * trace_slot] = globaltimer_ns();
-    __threadfence();
+    // the release is cumulative over what the CTA barrier above ordered before it: no separate fence (one costs 0.3 us here)
+    XP_LOG(c, 2560, 800, 98);
     asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.bar_ctr) : "memory");
+    XP_LOG(c, 2560, 800, 99);
     if (*c.go_count < (int)c.bar_epoch) go_wait_slow(c.go_count, (int)c.bar_epoch, c.s_abort, p.bar_ctr, p.status);
     __threadfence_block();   // the loader's acquire at GPU scope, its store of the count, this read and the barrier below form the chain
     if (p.trace && c.cta == 0) p.trace[2 * trace_slot + 1] = globaltimer_ns();
@@ -274,6 +280,7 @@ __device__ __forceinline__ void mma_resident(Ctx& c, const uint32_t* sl, int row
     for (int j = 0; j < 4; ++j) acc[t][j] = 0.f;
   // every warp waits for the stages of its K half, also a warp without rows: the stages are then handed back in step
   if (!a_wait(c, a_g0 + 2 * kh) || !a_wait(c, a_g0 + 2 * kh + 1)) *ok = false;
+  XP_MARK(c, 90);
   if (16 * mi >= rows || !*ok) {
     if (QUARTERS)
       for (int j = 0; j < 4; ++j) release_chunk(c, chunk_g0 + j);
@@ -391,6 +398,7 @@ __device__ __forceinline__ bool mma_streamed(Ctx& c, int rows, int K, float (&ac
       }
     }
     a_release(c, g);
+    XP_MARK(c, 91);
     if ((st & 3) == 3) release_chunk(c, c.chunk_g + (st >> 2));
   }
   c.a_g += (unsigned int)n_stages;
@@ -1010,7 +1018,10 @@ __device__ __forceinline__ void activation_producer_loop(Ctx& c) {
     }
     __threadfence_block();
     *c.go_count = phase;
-    fence_proxy_async_all();   // the rows were written through the generic proxy, the copies below read through the async one
+    XP_LOG(c, 3400, 300, 1);
+    // the rows were written to global memory through the generic proxy, the copies below read them through the async
+    // one: a proxy fence restricted to global memory (the unrestricted one costs 0.25 us more per phase)
+    asm volatile("fence.proxy.async.global;" ::: "memory");
   };
   // one stage = four 64-wide K blocks of MAX_ROWS rows from row0 on (rows past the tensor are filled with zeros), one copy
   auto stages = [&](const CUtensorMap* tm, int n_stages, int row0) {
@@ -1021,6 +1032,7 @@ __device__ __forceinline__ void activation_producer_loop(Ctx& c) {
       mbar_expect_tx(c.a_full + 8 * s, STAGE_BYTES);
       tma_load_3d(c.sbase + s * STAGE_BYTES, tm, c.a_full + 8 * s, 0, row0, st * 4, pol);
       ++g;
+      XP_LOG(c, 3400, 300, 2);
     }
   };
   const int nq = qkv_tile_count(c.cta, p.G);
@@ -1033,6 +1045,7 @@ __device__ __forceinline__ void activation_producer_loop(Ctx& c) {
       if (owner) stages(&p.tm_act, 4, 0);
     }
     for (int l = 0; l < p.nl && ok; ++l) {
+      c.fine = p.trace != nullptr && c.cta == 0 && step == 0 && l == 1;
       begin_phase();                                // QKV
       if (nq > 0) stages(&p.tm_xb, 4, 0);
       begin_phase();                                // attention: K, V and Q tiles of this CTA's work item
@@ -1095,6 +1108,7 @@ __global__ void __launch_bounds__(THREADS, 1) expert_persistent_kernel(const __g
   c.att_n = 0;
   c.bar_epoch = 0;
   c.fine = false;
+  c.nmark = 0;
   c.cta = blockIdx.x;
   c.tid = threadIdx.x;
   c.warp = threadIdx.x >> 5;
