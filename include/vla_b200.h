@@ -54,7 +54,9 @@ typedef struct vla_config {
                          bit 2: SigLIP attention on the legacy mma.sync kernel instead of tcgen05;
                          bit 3: prefix / suffix attention of batched forwards on the legacy mma.sync kernel;
                          bit 4: action expert as per-operator launches instead of the persistent kernel (which serves
-                                single-observation handles with at most 52 suffix tokens) */
+                                single-observation handles with at most 52 suffix tokens);
+                         bit 6: let the tiling model run GEMMs as tcgen05 CTA pairs (two CTAs share an activation tile,
+                                each loading half; off by default: measured no faster than single CTAs) */
 } vla_config;
 
 /* Replaces Pi0Inference.__init__ / Pi05Inference.__init__ up to buffer allocation (pi0_infer.py:1245-1317). */
@@ -171,7 +173,9 @@ const char* vla_last_error(vla_handle h);
  * epi: 0 = bf16 out (+bias, act: 0 none, 1 gelu-tanh, 2 silu, 3 GeGLU with W2), 1 = fp32 residual
  * (outf = res + bias + gate*acc, in place when res == outf), 2 = QKV+RoPE (N must be 2560; q, kcache, vcache out, vt = optional transposed value cache [256, vt_ld]).
  * split = cluster size along K (0 = library heuristic), bn = token tile (0 = heuristic), pair = two 128-feature
- * tiles of W per CTA sharing the activation tile (0 = heuristic, 1 = force, -1 = never; ignored with W2),
+ * tiles of W per CTA sharing the activation tile (0 = heuristic, 1 = force, -1 = never; ignored with W2), or
+ * 2 = tcgen05 CTA pairs: two CTAs on neighbouring feature tiles share the activation tile, each loading half of it
+ * (token tiles of 128 or 256, split <= 4; with W2 only unsplit 256-token tiles),
  * tok_tile = tokens per CTA (0 = heuristic: the token tiles are evened out; else a multiple of 32, <= bn). */
 typedef struct vla_gemm_desc {
   const void* x; int tokens; int K;

@@ -83,6 +83,16 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tm, uint32
       ::"r"(dst), "l"(tm), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
       : "memory");
 }
+// The same load issued by one CTA of a tcgen05 CTA pair: the destination is this CTA's shared memory, the mbarrier
+// (a shared::cluster address, see dsmem_map) may be the pair leader's.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tm, uint32_t bar_cluster, int c0, int c1,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(dst), "l"(tm), "r"(bar_cluster), "r"(c0), "r"(c1), "l"(policy)
+      : "memory");
+}
 // shared -> global tile store / fp32 reduce-add through TMA (bulk async-group completion)
 __device__ __forceinline__ void tma_store_2d(const void* tm, uint32_t src, int c0, int c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
@@ -137,6 +147,23 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// CTA-pair forms (cta_group::2): one thread of the pair's leader CTA (even cluster rank) issues an MMA of M = 256 whose
+// operands live in both CTAs' shared memory (A: 128 rows each, B: half of the N rows each, same offsets) and whose
+// accumulator rows 0-127 / 128-255 land in the two CTAs' tensor memory at the same address.
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the mbarrier at this shared-memory offset in every CTA of `cta_mask` (cluster ranks) once all MMAs
+// issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(cta_mask) : "memory");
+}
 // 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread (thread i = TMEM lane base+i).
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
   asm volatile(
@@ -180,6 +207,11 @@ __device__ __forceinline__ float dsmem_ld_f32(uint32_t addr) {
   float v;
   // volatile keeps it after the (volatile) cluster barrier; no memory clobber, so several loads can be in flight
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t dsmem_ld_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
   return v;
 }
 // Store into another CTA's shared memory; made visible to it by the next cluster barrier (release/acquire).

@@ -93,6 +93,8 @@ struct GemmParams {
   int tok_tile;      // tokens per CTA along grid.y, a multiple of 32 and <= BN (0 = BN): the host evens the tiles out
                      // (788 tokens = 4 x 224 rather than 3 x 256 + 20) so that the last tile does not stream the
                      // whole weight panel for a handful of tokens; the B box of tmB has this many rows
+  int cg2;           // launch of the CG2 variant (tcgen05 CTA pairs): gridDim.x = 2 * split, gridDim.z = pairs of feature
+                     // tiles, the B box of tmB has tok_tile / 2 rows
   int m256;          // launch of the PAIR variant: the two accumulators are two feature tiles of ONE weight
                      // (features feat0.. and feat0+128..) instead of the gate/up pair; each gets the plain epilogue
   int* status;       // device status word
@@ -103,11 +105,12 @@ struct GemmParams {
 
 constexpr int GEMM_THREADS = 320;
 
-// SPLITK variants are launched as clusters of `split` CTAs along K.
-template <int BN, bool DUAL, bool SPLITK>
+// SPLITK variants are launched as clusters of `split` CTAs along K.  CG2 variants run as tcgen05 CTA pairs: two
+// CTAs on neighbouring feature tiles share one activation tile, of which each loads half (see the kernel).
+template <int BN, bool DUAL, bool SPLITK, bool CG2 = false>
 struct GemmCfg {
   static constexpr int A_BYTES = 128 * 64 * 2;
-  static constexpr int B_BYTES = BN * 64 * 2;
+  static constexpr int B_BYTES = (CG2 ? BN / 2 : BN) * 64 * 2;
   static constexpr int STAGE_BYTES = A_BYTES * (DUAL ? 2 : 1) + B_BYTES;
   static constexpr int RECV_BYTES = 0;
   static constexpr int PARTIAL_FLOATS = 128 * BN * (DUAL ? 2 : 1);   // scratch floats per CTA
@@ -258,12 +261,18 @@ __device__ __forceinline__ void gemm_epilogue_cols(const GemmEpi& e, const EpiTh
 
 // DUAL: gate/up pair of two weights (GeGLU).  PAIR: two 128-feature tiles of one weight, each with the plain
 // epilogue.  Both keep two accumulators that share the activation tile (TWO).
-template <int BN, bool DUAL, bool SPLITK, bool PAIR = false>
+// CG2: the CTAs with blockIdx.x = 2 r and 2 r + 1 (neighbours in the cluster) form a tcgen05 CTA pair on the feature
+// tiles 2 z and 2 z + 1 of the same token tile and K slice r: each CTA brings in its own 128 x 64 weight tile and HALF of
+// the activation tile (the per-SM L2 read rate, ~60 B/clk, bounds a single CTA's 128 x 256 tile at 2/3 of the MMA
+// rate; the pair needs 2/3 of the bytes per MMA cycle), every load completes on the even CTA's barrier, whose MMA thread
+// issues cta_group::2 MMAs of M = 256 for both, and each CTA runs the unchanged epilogue on its own 128 accumulator rows.
+template <int BN, bool DUAL, bool SPLITK, bool PAIR = false, bool CG2 = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
   static_assert(!(DUAL && PAIR), "a paired launch has one weight");
+  static_assert(!(CG2 && PAIR), "CTA pairs take one feature tile per CTA");
   constexpr bool TWO = DUAL || PAIR;
   constexpr bool m256 = PAIR;
-  using C = GemmCfg<BN, TWO, SPLITK>;
+  using C = GemmCfg<BN, TWO, SPLITK, CG2>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -282,11 +291,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   KTRACE(10);
   if (threadIdx.x == 0) GEMM_TRACE(0);
   const int split = SPLITK ? p.split : 1;
-  const int rank = SPLITK ? (int)blockIdx.x : 0;  // == cluster rank: cluster dims are (split,1,1), gridDim.x == split
+  // cluster dims are (gridDim.x,1,1): blockIdx.x is the cluster rank = K slice, or 2 * K slice + rank in the CTA pair
+  const int pr = CG2 ? (int)(blockIdx.x & 1u) : 0;
+  const int rank = SPLITK ? (int)(CG2 ? blockIdx.x >> 1 : blockIdx.x) : 0;
   const int tok_tile = p.tok_tile > 0 ? p.tok_tile : BN;
   const int tok0 = blockIdx.y * tok_tile;
-  const uint32_t stage_tx = (uint32_t)(C::A_BYTES * (TWO ? 2 : 1) + tok_tile * 128);   // bytes one K block brings in
-  const int feat0 = blockIdx.z * (m256 ? 256 : 128);
+  // bytes one K block brings in (CG2: both CTAs' weight tiles and halves of the activation tile, counted by the leader)
+  const uint32_t stage_tx = CG2 ? (uint32_t)(2 * (C::A_BYTES * (TWO ? 2 : 1) + (tok_tile / 2) * 128))
+                                : (uint32_t)(C::A_BYTES * (TWO ? 2 : 1) + tok_tile * 128);
+  const int feat_tile = CG2 ? (int)blockIdx.z * 2 + pr : (int)blockIdx.z;
+  const int feat0 = feat_tile * (m256 ? 256 : 128);
   const int kb_begin = (int)(((long long)rank * p.k_blocks) / split);
   const int kb_end = (int)(((long long)(rank + 1) * p.k_blocks) / split);
   const int n_iters = kb_end - kb_begin;
@@ -313,6 +327,24 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) GEMM_TRACE(1);
+  // CTA pair: the peer's barriers must exist before anything signals them, and one MMA addresses the accumulators of
+  // both CTAs with one tensor-memory address, so the two allocations must have returned the same one (they do when each
+  // SM holds one CTA with tensor memory at a time; otherwise the launch gives up and says so in the status word).
+  uint32_t full_bar_lead = full_bar;   // shared::cluster address of the leader's full barriers
+  if (CG2) {
+    cluster_sync_all();
+    const uint32_t my_rank = cluster_ctarank();
+    full_bar_lead = dsmem_map(full_bar, my_rank & ~1u);
+    const uint32_t peer_base = dsmem_ld_u32(dsmem_map(smem_u32(tmem_slot), my_rank ^ 1u));
+    if (peer_base != tmem_base) {
+      if (threadIdx.x == 0) {
+        *abort_flag = 1;
+        if (p.status) atomicOr(p.status, VLA_ST_BAD_SHAPE);
+      }
+    }
+    __syncthreads();
+  }
+  const bool pair_ok = !CG2 || *abort_flag == 0;
 
   // Let the next kernels of the stream start now: their prologue and weight prefetch run under this kernel
   // (they block in their own griddepcontrol.wait until this grid has completed).
@@ -320,14 +352,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   // Weights do not depend on the previous kernel: fill the pipeline with weight tiles before waiting for it.
   const int n_pre = n_iters < C::STAGES ? n_iters : C::STAGES;
   uint64_t pol_w = 0;
-  if (warp == 0 && lane == 0) {
+  if (warp == 0 && lane == 0 && pair_ok) {
     pol_w = policy_evict_first();
     for (int it = 0; it < n_pre; ++it) {
       const uint32_t st = smem_base + it * C::STAGE_BYTES;
       const int k0 = (kb_begin + it) * 64;
-      mbar_expect_tx(full_bar + 8 * it, stage_tx);
-      tma_load_2d(st, &p.tmA, full_bar + 8 * it, k0, feat0, pol_w);
-      if (TWO) tma_load_2d(st + C::A_BYTES, m256 ? &p.tmA : &p.tmA2, full_bar + 8 * it, k0, feat0 + (m256 ? 128 : 0), pol_w);
+      if (pr == 0) mbar_expect_tx(full_bar + 8 * it, stage_tx);
+      if (CG2) {
+        tma_load_2d_pair(st, &p.tmA, full_bar_lead + 8 * it, k0, feat0, pol_w);
+        if (TWO) tma_load_2d_pair(st + C::A_BYTES, &p.tmA2, full_bar_lead + 8 * it, k0, feat0, pol_w);
+      } else {
+        tma_load_2d(st, &p.tmA, full_bar + 8 * it, k0, feat0, pol_w);
+        if (TWO) tma_load_2d(st + C::A_BYTES, m256 ? &p.tmA : &p.tmA2, full_bar + 8 * it, k0, feat0 + (m256 ? 128 : 0), pol_w);
+      }
     }
   }
   // Activations (and everything the epilogue reads or writes) do.
@@ -336,8 +373,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   if (threadIdx.x == 0) GEMM_TRACE(2);
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (lane == 0 && pair_ok) {
       const uint64_t pol_x = policy_evict_last();
+      const int tok_b = CG2 ? tok0 + pr * (umma_n >> 1) : tok0;   // CTA pair: rows [0, N/2) and [N/2, N) of the tile
       for (int it = 0; it < n_iters; ++it) {
         const int s = it % C::STAGES;
         const uint32_t st = smem_base + s * C::STAGE_BYTES;
@@ -345,19 +383,26 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         if (it >= n_pre) {
           const uint32_t ph = (uint32_t)(it / C::STAGES) & 1u;
           if (!mbar_wait(empty_bar + 8 * s, ph ^ 1u, abort_flag)) break;
-          mbar_expect_tx(full_bar + 8 * s, stage_tx);
-          tma_load_2d(st, &p.tmA, full_bar + 8 * s, k0, feat0, pol_w);
-          if (TWO) tma_load_2d(st + C::A_BYTES, m256 ? &p.tmA : &p.tmA2, full_bar + 8 * s, k0, feat0 + (m256 ? 128 : 0), pol_w);
+          if (pr == 0) mbar_expect_tx(full_bar + 8 * s, stage_tx);
+          if (CG2) {
+            tma_load_2d_pair(st, &p.tmA, full_bar_lead + 8 * s, k0, feat0, pol_w);
+            if (TWO) tma_load_2d_pair(st + C::A_BYTES, &p.tmA2, full_bar_lead + 8 * s, k0, feat0, pol_w);
+          } else {
+            tma_load_2d(st, &p.tmA, full_bar + 8 * s, k0, feat0, pol_w);
+            if (TWO) tma_load_2d(st + C::A_BYTES, m256 ? &p.tmA : &p.tmA2, full_bar + 8 * s, k0, feat0 + (m256 ? 128 : 0), pol_w);
+          }
         }
-        tma_load_2d(st + C::A_BYTES * (TWO ? 2 : 1), &p.tmB, full_bar + 8 * s, k0, tok0, pol_x);
+        if (CG2) tma_load_2d_pair(st + C::A_BYTES * (TWO ? 2 : 1), &p.tmB, full_bar_lead + 8 * s, k0, tok_b, pol_x);
+        else tma_load_2d(st + C::A_BYTES * (TWO ? 2 : 1), &p.tmB, full_bar + 8 * s, k0, tok0, pol_x);
       }
       GEMM_TRACE(3);
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0) {
-      // instruction descriptor: D=f32, A=B=bf16, both K-major, N = umma_n, M = 128
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(umma_n >> 3) << 17) | (8u << 24);
+    if (lane == 0 && pr == 0 && pair_ok) {
+      // instruction descriptor: D=f32, A=B=bf16, both K-major, N = umma_n, M = 128 (256 over a CTA pair)
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(umma_n >> 3) << 17) | ((CG2 ? 16u : 8u) << 24);
+      const uint16_t pair_mask = (uint16_t)(3u << (CG2 ? (cluster_ctarank() & ~1u) : 0u));
       bool ok = true;
       for (int it = 0; it < n_iters && ok; ++it) {
         const int s = it % C::STAGES;
@@ -374,12 +419,22 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           const uint32_t acc = (it | kk) != 0;
-          umma_bf16(tmem_base, da + 2 * kk, db + 2 * kk, idesc, acc);
-          if (TWO) umma_bf16(tmem_base + BN, da2 + 2 * kk, db + 2 * kk, idesc, acc);
+          if (CG2) {
+            umma_bf16_pair(tmem_base, da + 2 * kk, db + 2 * kk, idesc, acc);
+            if (TWO) umma_bf16_pair(tmem_base + BN, da2 + 2 * kk, db + 2 * kk, idesc, acc);
+          } else {
+            umma_bf16(tmem_base, da + 2 * kk, db + 2 * kk, idesc, acc);
+            if (TWO) umma_bf16(tmem_base + BN, da2 + 2 * kk, db + 2 * kk, idesc, acc);
+          }
         }
-        umma_commit(empty_bar + 8 * s);  // frees this smem stage once the MMAs have read it
+        // frees this smem stage (in both CTAs of a pair) once the MMAs have read it
+        if (CG2) umma_commit_pair(empty_bar + 8 * s, pair_mask);
+        else umma_commit(empty_bar + 8 * s);
       }
-      if (ok) umma_commit(tmem_full_bar);
+      if (ok) {
+        if (CG2) umma_commit_pair(tmem_full_bar, pair_mask);
+        else umma_commit(tmem_full_bar);
+      }
       GEMM_TRACE(5);
     }
     __syncwarp();
@@ -569,7 +624,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     constexpr int ACCS = TWO ? 2 : 1;
     const int n_cols = min(umma_n, p.n_tok - tok0);
     // scratch of this cluster: [src rank][accumulator][column][128 features]
-    float* tile_scratch = p.scratch + (size_t)(blockIdx.z * gridDim.y + blockIdx.y) * split * C::PARTIAL_FLOATS;
+    float* tile_scratch = p.scratch + (size_t)(feat_tile * gridDim.y + blockIdx.y) * split * C::PARTIAL_FLOATS;
     if (is_epi && acc_ok) {
       float* mine = tile_scratch + (size_t)rank * C::PARTIAL_FLOATS;
       for (int c0 = 32 * half; c0 < umma_n; c0 += 64) {
@@ -632,6 +687,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   // ---------------- teardown ----------------
   if (threadIdx.x == 64) GEMM_TRACE(11);
   tc_fence_before();
+  if (CG2) cluster_sync_all();   // neither CTA of a pair retires while the other may still signal its barriers
   __syncthreads();
   if (threadIdx.x == 0) GEMM_TRACE(12);
   if (*abort_flag) {

@@ -176,8 +176,8 @@ struct GemmOp {
 bool can_split(int, bool) { return true; }
 
 // Scratch floats a GEMM launch needs for its split-K partial tiles (0 without split).
-size_t gemm_scratch_floats(int bn, bool dual, dim3 grid) {
-  if (grid.x <= 1) return 0;
+size_t gemm_scratch_floats(int bn, bool dual, dim3 grid, int cg2 = 0) {
+  if (grid.x <= (cg2 ? 2u : 1u)) return 0;
   return (size_t)grid.x * grid.y * grid.z * 128 * bn * (dual ? 2 : 1);
 }
 
@@ -199,9 +199,13 @@ int pick_split(int units, int k_blocks, int sm_count) {
 // accumulators sharing the activation tile like the gate/up pair): 32 KB + 128 B per token per K block for twice
 // the MMA work, which lifts 256-token tiles from TMA-bound (96 B/clk) to balanced (64 B/clk) at the price of half
 // as many CTAs and a twice larger split-K exchange.  m256_mode: 0 = let the model choose, 1 = force, -1 = never.
+// A third shape, cg2, runs neighbouring feature tiles as tcgen05 CTA pairs that share the activation tile, each CTA
+// loading half of it (16 KB + 64 B per token per K block and CTA): same CTA count and exchange as the plain shape.
+// cg2_mode: 0 = let the model choose, 1 = force, -1 = never.
 void pick_tiling(int tokens, int feat_tiles, int k_blocks, bool dual, int sm_count, int* bn, int* split, int* m256,
-                 int m256_mode = 0) {
+                 int m256_mode = 0, int* cg2 = nullptr, int cg2_mode = 0) {
   *m256 = 0;
+  if (cg2) *cg2 = 0;
   if (tokens <= 128 && m256_mode <= 0) {
     *bn = tokens <= 64 ? 64 : 128;
     *split = pick_split(feat_tiles, k_blocks, sm_count);
@@ -213,14 +217,19 @@ void pick_tiling(int tokens, int feat_tiles, int k_blocks, bool dual, int sm_cou
   // up to 256 tokens a 128-token tile always measured at least as fast as one 256-token tile (more CTAs, a
   // cheaper split-K exchange); dual-accumulator GEMMs keep 256 (their main loop is MMA-bound only there)
   const int b_max = (tokens <= 256 && !dual) ? 128 : 256;
-  for (int pair = 0; pair <= 1; ++pair) {
+  for (int shape = 0; shape <= 2; ++shape) {   // 0 plain, 1 paired feature tiles in one CTA, 2 CTA pairs
+    const int pair = shape == 1, two = shape == 2;
     if (pair && (dual || m256_mode < 0 || feat_tiles < 2)) continue;
     if (!pair && m256_mode > 0 && !dual && feat_tiles >= 2) continue;
+    if (two && (!cg2 || cg2_mode < 0 || feat_tiles < 2)) continue;
+    if (!two && cg2 && cg2_mode > 0 && feat_tiles >= 2) continue;
     const int accs = (dual || pair) ? 2 : 1;
-    const int ftiles = pair ? (feat_tiles + 1) / 2 : feat_tiles;
-    for (int b = 128; b <= (pair ? 256 : b_max); b *= 2) {
-      for (int s = 1; s <= 8; s *= 2) {
+    const int ftiles = pair ? (feat_tiles + 1) / 2 : (two ? (feat_tiles + 1) / 2 * 2 : feat_tiles);
+    for (int b = 128; b <= ((pair || two) ? 256 : b_max); b *= 2) {
+      if (two && dual && b != 256) continue;              // the dual CTA-pair kernel exists for 256-token tiles only
+      for (int s = 1; s <= (two ? 4 : 8); s *= 2) {       // a cluster holds at most 8 CTAs
         if (s > 1 && (k_blocks / s < 8)) continue;          // keep K slices long enough to amortise the exchange
+        if (two && dual && s > 1) continue;
         const int tok_tiles = (tokens + b - 1) / b;
         const long long ctas = (long long)ftiles * tok_tiles * s;
         if (s > 1 && (size_t)ctas * 128 * b * accs > ((size_t)16 << 20)) continue;   // split-K scratch capacity (floats)
@@ -228,7 +237,7 @@ void pick_tiling(int tokens, int feat_tiles, int k_blocks, bool dual, int sm_cou
         // took 72 us paired with K split 4 against 68 us unpaired, 17 024 tokens 870 us against 1 076 us)
         if (pair && m256_mode == 0 && (s > 1 || ctas < 2LL * sm_count)) continue;
         const int kb = (k_blocks + s - 1) / s;
-        const double load = kb * (16384.0 * accs + 128.0 * b) / 64.0;
+        const double load = kb * (16384.0 * accs + (two ? 64.0 : 128.0) * b) / 64.0;
         const double mma = kb * 2.0 * b * accs;
         const double epi = 22.0 * (b / 2) * accs;
         // partial tile through L2 + cluster barrier; measured cheaper than twice the 128-token figure for a 4-way
@@ -237,26 +246,31 @@ void pick_tiling(int tokens, int feat_tiles, int k_blocks, bool dual, int sm_cou
         const double cta = (load > mma ? load : mma) + epi + exch;
         // clusters are scheduled whole within a GPC: 144 CTAs in clusters of 4 measured like two waves
         // (512 x 4304 x 1152: 29 us against 25 us for 72 CTAs), so 4- and 8-CTA clusters count 128 resident CTAs
-        const int resident = s >= 4 ? 128 : sm_count;
+        const int resident = s * (two ? 2 : 1) >= 4 ? 128 : sm_count;
         const double waves = (double)((ctas + resident - 1) / resident);
         const double cost = waves * cta;
-        if (cost < best) { best = cost; *bn = b; *split = s; *m256 = pair; }
+        if (cost < best) { best = cost; *bn = b; *split = s; *m256 = pair; if (cg2) *cg2 = two; }
       }
     }
   }
 }
 
-template <int BN, bool DUAL, bool SPLITK, bool PAIR = false>
+template <int BN, bool DUAL, bool SPLITK, bool PAIR = false, bool CG2 = false>
 cudaError_t launch_gemm_t(const GemmOp& op, cudaStream_t st, bool pdl) {
-  using C = GemmCfg<BN, DUAL || PAIR, SPLITK>;
+  using C = GemmCfg<BN, DUAL || PAIR, SPLITK, CG2>;
   static_assert(C::VALID, "tile shape leaves fewer than 3 pipeline stages");
-  auto kern = gemm_sm100_kernel<BN, DUAL, SPLITK, PAIR>;
+  auto kern = gemm_sm100_kernel<BN, DUAL, SPLITK, PAIR, CG2>;
   if (cudaError_t e = ensure_smem_attr(reinterpret_cast<const void*>(kern), C::SMEM_BYTES); e != cudaSuccess) return e;
-  return launch_ex(kern, op.grid, dim3(GEMM_THREADS), C::SMEM_BYTES, st, op.p.split, pdl, op.p);
+  return launch_ex(kern, op.grid, dim3(GEMM_THREADS), C::SMEM_BYTES, st, op.p.split * (CG2 ? 2 : 1), pdl, op.p);
 }
 
 cudaError_t launch_gemm(const GemmOp& op, cudaStream_t st, bool pdl) {
   const bool sk = op.p.split > 1;
+  if (op.p.cg2) {    // CTA pairs (built for 128- and 256-token tiles; dual only unsplit at 256)
+    if (op.dual) return launch_gemm_t<256, true, false, false, true>(op, st, pdl);
+    if (op.bn == 128) return sk ? launch_gemm_t<128, false, true, false, true>(op, st, pdl) : launch_gemm_t<128, false, false, false, true>(op, st, pdl);
+    return sk ? launch_gemm_t<256, false, true, false, true>(op, st, pdl) : launch_gemm_t<256, false, false, false, true>(op, st, pdl);
+  }
   if (op.p.m256) {   // two feature tiles of one weight per CTA
     if (op.bn == 64) return sk ? launch_gemm_t<64, false, true, true>(op, st, pdl) : launch_gemm_t<64, false, false, true>(op, st, pdl);
     if (op.bn == 128) return sk ? launch_gemm_t<128, false, true, true>(op, st, pdl) : launch_gemm_t<128, false, false, true>(op, st, pdl);
@@ -277,21 +291,31 @@ cudaError_t launch_gemm(const GemmOp& op, cudaStream_t st, bool pdl) {
 // w / w2: repacked weights [n_feat_pad, Kp]; x: activations [tokens, K] with pitch ldx.
 bool build_gemm(GemmOp* op, const bf16* w, const bf16* w2, int n_feat, int n_feat_pad, int Kp, const bf16* x, int tokens,
                 int Kx, int ldx, const GemmEpi& epi, int* status, int sm_count, int force_bn, int force_split,
-                std::string* err, int m256_mode = 0, int force_tok_tile = 0) {
+                std::string* err, int m256_mode = 0, int force_tok_tile = 0, int cg2_mode = 0) {
   memset(op, 0, sizeof *op);
   op->dual = w2 != nullptr;
   if (Kp % 64 || n_feat_pad % 128) { *err = "repacked weight must be padded to 128 features x 64 K"; return false; }
   int feat_tiles = n_feat_pad / 128;
   const int kb = Kp / 64;
-  int bn, split, m256;
-  pick_tiling(tokens, feat_tiles, kb, op->dual, sm_count, &bn, &split, &m256, m256_mode);
+  int bn, split, m256, cg2;
+  pick_tiling(tokens, feat_tiles, kb, op->dual, sm_count, &bn, &split, &m256, m256_mode, &cg2, cg2_mode);
   if (force_bn > 0) {
     bn = force_bn;
     if (bn != 64 && bn != 128 && bn != 256) { *err = "token tile must be 64, 128 or 256"; return false; }
     m256 = (m256_mode > 0 && !op->dual && feat_tiles >= 2) ? 1 : 0;
+    cg2 = (cg2_mode > 0 && feat_tiles >= 2) ? 1 : 0;
     split = can_split(bn, op->dual) ? pick_split((m256 ? (feat_tiles + 1) / 2 : feat_tiles) * ((tokens + bn - 1) / bn), kb, sm_count) : 1;
+    if (cg2 && split > 4) split = 4;
   }
   if (force_split > 0) split = force_split;
+  if (cg2) {
+    if (m256) { *err = "a launch is either paired feature tiles or CTA pairs"; return false; }
+    if (bn == 64 || (op->dual && (bn != 256 || split > 1)) || split > 4) {
+      *err = "CTA pairs: 128- or 256-token tiles, K split <= 4; two weights only unsplit with 256-token tiles";
+      return false;
+    }
+  }
+  op->p.cg2 = cg2;
   if (m256) {
     op->dual = true;                       // two accumulators, both fed from `w`
     feat_tiles = (feat_tiles + 1) / 2;
@@ -315,7 +339,7 @@ bool build_gemm(GemmOp* op, const bf16* w, const bf16* w2, int n_feat, int n_fea
   if (split > 8 || split > kb || (split & (split - 1))) { *err = "split must be 1, 2, 4 or 8 and <= K/64"; return false; }
   if (!make_tmap(&op->p.tmA, w, Kp, n_feat_pad, Kp, 128, err)) return false;
   if (w2 && !make_tmap(&op->p.tmA2, w2, Kp, n_feat_pad, Kp, 128, err)) return false;
-  if (!make_tmap(&op->p.tmB, x, Kx, tokens, ldx, tok_tile, err)) return false;
+  if (!make_tmap(&op->p.tmB, x, Kx, tokens, ldx, cg2 ? tok_tile / 2 : tok_tile, err)) return false;
   op->p.n_feat = n_feat;
   op->p.n_tok = tokens;
   op->p.k_blocks = kb;
@@ -340,7 +364,7 @@ bool build_gemm(GemmOp* op, const bf16* w, const bf16* w2, int n_feat, int n_fea
   }
   op->p.status = status;
   op->p.epi = epi;
-  op->grid = dim3(split, tok_tiles, feat_tiles);
+  op->grid = cg2 ? dim3(2 * split, tok_tiles, (feat_tiles + 1) / 2) : dim3(split, tok_tiles, feat_tiles);
   return true;
 }
 
@@ -729,12 +753,13 @@ struct Plan {
     const bf16* w2 = key2 ? m->W.at(key2).w + (size_t)layer * e.Np * e.Kp : nullptr;
     GemmOp op;
     const int n_feat = n_feat_override > 0 ? n_feat_override : e.spec.N;
-    if (!build_gemm(&op, w, w2, n_feat, e.Np, e.Kp, x, tokens, Kx, ldx, epi, m->d_status, m->sm_count, 0, 0, &err)) {
+    if (!build_gemm(&op, w, w2, n_feat, e.Np, e.Kp, x, tokens, Kx, ldx, epi, m->d_status, m->sm_count, 0, 0, &err, 0, 0,
+                    (m->cfg.flags & 64) ? 0 : -1)) {
       ok = false;
       err = std::string(key) + ": " + err;
       return;
     }
-    if (gemm_scratch_floats(op.bn, op.dual, op.grid) > m->gemm_scratch_cap) {
+    if (gemm_scratch_floats(op.bn, op.dual, op.grid, op.p.cg2) > m->gemm_scratch_cap) {
       ok = false;
       err = std::string(key) + ": split-K scratch too small";
       return;
@@ -1754,13 +1779,13 @@ int vla_op_gemm(const vla_gemm_desc* d, void* stream) {
     e.vt = reinterpret_cast<bf16*>(d->vt); e.vt_ld = d->vt_ld;
   }
   if (!build_gemm(&op, wt, wt2, d->N, Np, Kp, reinterpret_cast<const bf16*>(d->x), d->tokens, d->K, d->K, e, status, sms,
-                  d->bn, d->split, &err, d->pair, d->tok_tile)) {
+                  d->bn, d->split, &err, d->pair == 2 ? -1 : d->pair, d->tok_tile, d->pair == 2 ? 1 : (d->pair == 0 ? 0 : -1))) {
     g_last_error = err;
     rc = VLA_ERR_SHAPE;
     goto done;
   }
-  if (gemm_scratch_floats(op.bn, op.dual, op.grid) > 0) {
-    CKG(cudaMalloc(&scratch, gemm_scratch_floats(op.bn, op.dual, op.grid) * sizeof(float)));
+  if (gemm_scratch_floats(op.bn, op.dual, op.grid, op.p.cg2) > 0) {
+    CKG(cudaMalloc(&scratch, gemm_scratch_floats(op.bn, op.dual, op.grid, op.p.cg2) * sizeof(float)));
     op.p.scratch = scratch;
   }
   CKG(launch_gemm(op, st, false));
@@ -1930,15 +1955,15 @@ int vla_op_gemm_noalloc(const vla_gemm_noalloc_desc* d, void* stream) {
   int split = d->split;
   for (;;) {
     if (!build_gemm(&op, reinterpret_cast<const bf16*>(d->w_nk), nullptr, d->N, d->n_pad, d->k_pad,
-                    reinterpret_cast<const bf16*>(d->x), d->tokens, d->K, d->K, e, nd->status, sms, 0, split, &err, -1)) {
+                    reinterpret_cast<const bf16*>(d->x), d->tokens, d->K, d->K, e, nd->status, sms, 0, split, &err, -1, 0, -1)) {
       g_last_error = "vla_op_gemm_noalloc: " + err;
       return VLA_ERR_SHAPE;
     }
-    if (gemm_scratch_floats(op.bn, op.dual, op.grid) <= VLA_NOALLOC_SCRATCH_FLOATS) break;
+    if (gemm_scratch_floats(op.bn, op.dual, op.grid, op.p.cg2) <= VLA_NOALLOC_SCRATCH_FLOATS) break;
     if (d->split != 0 || op.p.split <= 1) {
       char buf[200];
       snprintf(buf, sizeof buf, "vla_op_gemm_noalloc: this shape needs %zu scratch floats, the built-in scratch holds %u; "
-               "use a smaller split or vla_op_gemm", gemm_scratch_floats(op.bn, op.dual, op.grid), VLA_NOALLOC_SCRATCH_FLOATS);
+               "use a smaller split or vla_op_gemm", gemm_scratch_floats(op.bn, op.dual, op.grid, op.p.cg2), VLA_NOALLOC_SCRATCH_FLOATS);
       g_last_error = buf;
       return VLA_ERR_LIMIT;
     }

@@ -171,6 +171,59 @@ def test_gemm_pair_residual(tokens, K, N, split, gated):
     assert_close(out, res + bias + (y * gate if gated else y), rel=1e-4, what="paired residual")
 
 
+# tcgen05 CTA pairs (pair=2): two CTAs on neighbouring feature tiles share the activation tile, each loading half of it.
+# Ragged token tiles (788 = 4 x 224 with a 116-token tail), an odd number of feature tiles (the last pair's second CTA
+# has no features), every K split, and every epilogue the forward uses with them.
+@pytest.mark.parametrize("tokens,K,N,split,bn", [(788, 2048, 2048, 1, 256), (788, 4096, 2048, 2, 256), (768, 4352, 1152, 4, 256),
+                                                 (300, 1152, 1152, 2, 128), (256, 1152, 4304, 1, 256), (600, 2048, 384, 1, 128),
+                                                 (768, 1152, 3456, 1, 256), (130, 2048, 1024, 4, 128), (256, 16384, 2048, 4, 128)])
+def test_gemm_cta_pair_bias_bf16(tokens, K, N, split, bn):
+    import vla_ops as gpu_ops
+    d = dev()
+    x, w, b = rnd((tokens, K), 1.0, 72, d), rnd((K, N), 0.05, 73, d), rnd((N,), 0.5, 74, d).float()
+    out = gpu_ops.gemm(x, w, bias=b, split=split, bn=bn, pair=2)
+    assert_close(out, x.float() @ w.float() + b, what="CTA-pair gemm+bias")
+
+
+@pytest.mark.parametrize("tokens,K,N,split,gated", [(788, 16384, 2048, 2, False), (788, 2048, 2048, 1, True), (1576, 4304, 1152, 1, False),
+                                                    (768, 4304, 1152, 4, False)])
+def test_gemm_cta_pair_residual(tokens, K, N, split, gated):
+    import vla_ops as gpu_ops
+    d = dev()
+    x, w = rnd((tokens, K), 1.0, 75, d), rnd((K, N), 0.02, 76, d)
+    res = rnd((tokens, N), 1.0, 77, d).float()
+    gate = rnd((N,), 1.0, 78, d).float() if gated else None
+    bias = rnd((N,), 0.5, 79, d).float()
+    out = gpu_ops.gemm(x, w, bias=bias, epi=1, res=res, gate=gate, split=split, bn=256, pair=2)
+    y = x.float() @ w.float()
+    assert_close(out, res + bias + (y * gate if gated else y), rel=1e-4, what="CTA-pair residual")
+
+
+@pytest.mark.parametrize("tokens,K,N", [(788, 2048, 1024), (256, 2048, 512), (564, 2048, 16384)])
+def test_gemm_cta_pair_geglu(tokens, K, N):
+    import vla_ops as gpu_ops
+    d = dev()
+    x, wg, wu = rnd((tokens, K), 1.0, 80, d), rnd((K, N), 0.03, 81, d), rnd((K, N), 0.03, 82, d)
+    ref = O.gelu_tanh(x.float() @ wg.float()) * (x.float() @ wu.float())
+    assert_close(gpu_ops.gemm(x, wg, w2=wu, act=3, split=1, bn=256, pair=2), ref, what="CTA-pair geglu")
+
+
+@pytest.mark.parametrize("tokens,split,bn", [(788, 1, 256), (256, 2, 128), (564, 1, 256)])
+def test_gemm_cta_pair_qkv_rope(tokens, split, bn):
+    import vla_ops as gpu_ops
+    d = dev()
+    x, w = rnd((tokens, 2048), 1.0, 83, d), rnd((2048, 2560), 0.03, 84, d)
+    q, kc, vc, vt = gpu_ops.gemm(x, w, epi=2, split=split, bn=bn, pair=2,
+                                 qkv=dict(kv_rows=tokens, pos_off=0, rows_per_obs=tokens, kv_obs_stride=tokens, kv_row_off=0))
+    y = x.float() @ w.float()
+    cos, sin = O.rope_table(torch.arange(tokens, device=d))
+    qr = O.apply_rope(y[:, :2048].reshape(tokens, 8, 256).transpose(0, 1), cos, sin).transpose(0, 1).reshape(tokens, 2048)
+    assert_close(q, qr, what="Q")
+    assert_close(kc, O.apply_rope(y[:, 2048:2304], cos, sin), what="K")
+    assert_close(vc, y[:, 2304:], what="V")
+    assert_close(vt[:, :tokens].t(), y[:, 2304:], what="V transposed")
+
+
 @pytest.mark.parametrize("act", [1, 2])
 def test_gemm_activation(act):
     import vla_ops as gpu_ops
