@@ -329,6 +329,19 @@ bool build_gemm(GemmOp* op, const bf16* w, const bf16* w2, int n_feat, int n_fea
     const int n_tiles = (tokens + bn - 1) / bn;
     tok_tile = std::min(bn, (((tokens + n_tiles - 1) / n_tiles) + 31) / 32 * 32);
   }
+  // A launch that fits the SMs in one wave with room to spare takes more, smaller token tiles (multiples of 32) until
+  // the wave is full: the K loop of a CTA is bound by its MMAs (2 clk per token and 16-wide K step) or by the bytes it
+  // pulls from L2, both of which shrink with the tile (SigLIP QKV at 768 tokens: 27 feature tiles x 3 token tiles of
+  // 256 = 81 CTAs become 27 x 5 tiles of 160 = 135 CTAs).
+  if (tokens >= 192 && !m256) {
+    const int per_tok_tile = (cg2 ? 2 * ((feat_tiles + 1) / 2) : feat_tiles) * split;
+    const int resident = split * (cg2 ? 2 : 1) >= 4 ? 128 : sm_count;
+    int n_tiles = (tokens + tok_tile - 1) / tok_tile;
+    if (per_tok_tile * n_tiles <= resident) {
+      n_tiles = std::min(std::max(n_tiles, resident / per_tok_tile), (tokens + 31) / 32);
+      tok_tile = std::min(tok_tile, ((tokens + n_tiles - 1) / n_tiles + 31) / 32 * 32);
+    }
+  }
   if (force_tok_tile > 0) {
     if (force_tok_tile % 32 || force_tok_tile > bn) { *err = "token tile stride must be a multiple of 32 and <= bn"; return false; }
     tok_tile = force_tok_tile;
