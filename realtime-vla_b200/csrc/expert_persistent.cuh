@@ -44,6 +44,7 @@ constexpr int N_OWNERS = 128;         // CTAs that own 8 features of the 1024-wi
 constexpr int CH_PER_LAYER = 17;      // stream slots per layer: qkv 0-2, o 3-4, (gate,up) x4 5-12, down 13-16
 constexpr int ATT_ROWS = 32;          // query rows per attention work item
 constexpr int ATT_MAX_KEYS = 96;      // keys per split
+constexpr int MRG_BATCH = 12;         // key splits merged per round of loads
 constexpr int ATT_V_OFF = ATT_MAX_KEYS * 512;     // V tiles behind the K tiles
 constexpr int ATT_Q_OFF = 2 * ATT_MAX_KEYS * 512; // Q tiles (16 KB) fill the rest of the activation region
 
@@ -127,7 +128,7 @@ struct Ctx {
   const Params* p;
   uint32_t sbase;         // shared address of the activation region (1024-aligned)
   uint8_t* sptr;          // generic pointer to the same
-  uint32_t w_full, w_empty, a_full, a_empty, att_full;
+  uint32_t w_full, w_empty, a_full, a_empty, att_full, att_full_v;   // att_full: Q and K tiles, att_full_v: V tiles
   volatile int* go_count; // grid barriers passed, published by thread 0 for the activation warp
   volatile int* s_abort;
   float* fs;              // [64] per-token RMS scale
@@ -413,13 +414,15 @@ struct ResidEpi {
   int rows;          // valid A rows
   int row_off;       // output token = A row + row_off
   bool accumulate;   // x += gate * acc (else x = acc + bias)
+  bool store_x;      // also write the fp32 stream to global memory (nothing in the kernel reads it: only the state after the
+                     // last layer of a step is kept for inspection)
   float b0, b1, g0, g1, m0, m1;   // bias, gate and mirror scale (1 + adaRMS scale of the consuming norm) of features n, n+1
 };
 __device__ __forceinline__ ResidEpi make_resid(Ctx& c, int rows, int row_off, bool accumulate, const float* bias, const float* gate,
                                                const float* mscale) {
   const int n = 8 * c.cta + 2 * (c.lane & 3);
   ResidEpi e;
-  e.rows = rows; e.row_off = row_off; e.accumulate = accumulate;
+  e.rows = rows; e.row_off = row_off; e.accumulate = accumulate; e.store_x = false;
   e.b0 = bias ? bias[n] : 0.f; e.b1 = bias ? bias[n + 1] : 0.f;
   e.g0 = gate ? gate[n] : 1.f; e.g1 = gate ? gate[n + 1] : 1.f;
   e.m0 = mscale ? 1.f + mscale[n] : 1.f; e.m1 = mscale ? 1.f + mscale[n + 1] : 1.f;
@@ -447,7 +450,7 @@ __device__ __forceinline__ void epi_resid(Ctx& c, const ResidEpi& e, const float
       c.xs[t * 8 + j0] = v0;
       c.xs[t * 8 + j0 + 1] = v1;
       *reinterpret_cast<uint32_t*>(p.xb + (size_t)t * 1024 + n) = pack_bf16x2(v0 * e.m0, v1 * e.m1);
-      *reinterpret_cast<float2*>(p.x_out + (size_t)t * 1024 + n) = make_float2(v0, v1);
+      if (e.store_x) *reinterpret_cast<float2*>(p.x_out + (size_t)t * 1024 + n) = make_float2(v0, v1);
     }
     float sq = v0 * v0 + v1 * v1;
     sq += __shfl_xor_sync(0xffffffffu, sq, 1);
@@ -534,7 +537,6 @@ __device__ __forceinline__ bool phase_action_mlp(Ctx& c) {
     const float v = c.sttok[c.tid];
     c.xs[c.tid] = v;
     p.xb[8 * c.cta + c.tid] = __float2bfloat16(v);
-    p.x_out[8 * c.cta + c.tid] = v;
     float sq = v * v;
     sq += __shfl_xor_sync(0xffu, sq, 1);
     sq += __shfl_xor_sync(0xffu, sq, 2);
@@ -661,12 +663,13 @@ __device__ __forceinline__ bool phase_geglu(Ctx& c, int step, int layer) {
 }
 
 // Attention-out (K = 2048) and MLP-down (K = 4096) projections with the residual add.
-__device__ __forceinline__ bool phase_resid(Ctx& c, int K, const float* gate, const float* mscale) {
+__device__ __forceinline__ bool phase_resid(Ctx& c, int K, const float* gate, const float* mscale, bool store_x) {
   const Params& p = *c.p;
   ssq_rotate(c);
   if (c.cta >= N_OWNERS) { ++c.pk; return true; }
   XP_MARK(c, K == 2048 ? 20 : 40);
-  const ResidEpi e = make_resid(c, p.S, 0, true, nullptr, gate, mscale);
+  ResidEpi e = make_resid(c, p.S, 0, true, nullptr, gate, mscale);
+  e.store_x = store_x;
   float acc[1][4];
   const bool ok = mma_streamed(c, p.S, K, acc);
   XP_MARK(c, K == 2048 ? 21 : 41);
@@ -740,8 +743,7 @@ __device__ __forceinline__ bool phase_attention(Ctx& c, int layer) {
   const uint32_t sP = c.sbase + A_BYTES;                      // bf16 [32][104] (pitch 208 B)
   float* red = reinterpret_cast<float*>(c.sptr + A_BYTES + 32 * 208);   // rmax[4][32], rsum[4][32]
   XP_MARK(c, 10);
-  const bool ok = wait_bar(c, c.att_full, c.att_n & 1u);
-  ++c.att_n;
+  bool ok = wait_bar(c, c.att_full, c.att_n & 1u);   // Q and K; the V tiles are waited for in front of the PV product
   XP_MARK(c, 11);
 
   const int mi = c.warp & 1, grp = c.warp >> 1;     // 16-row tile, key group (S) / 64-dim group (O)
@@ -846,6 +848,8 @@ __device__ __forceinline__ bool phase_attention(Ctx& c, int layer) {
   }
   cbar();
   XP_MARK(c, 13);
+  if (!wait_bar(c, c.att_full_v, c.att_n & 1u)) ok = false;
+  ++c.att_n;
   // ---- O = P V for dims 64 grp .. 64 grp + 63 (one 64-dim V block per warp group) ----
   float o[8][4];
 #pragma unroll
@@ -903,7 +907,8 @@ __device__ __forceinline__ bool phase_attention(Ctx& c, int layer) {
 }
 
 // Suffix attention, part 2: rows are dealt round-robin to the CTAs; a warp pair merges one row (each lane 4 dims) over
-// the key splits, with every load of a batch of 8 splits issued before the first use.
+// the key splits, with every load of a batch of MRG_BATCH splits issued before the first use (one L2 round trip for the
+// usual 11 splits of 788 prefix + 51 suffix keys).
 __device__ __forceinline__ void phase_attention_merge(Ctx& c) {
   const Params& p = *c.p;
   const int R = p.S * 8, ks = p.att_ks;
@@ -915,24 +920,24 @@ __device__ __forceinline__ void phase_attention_merge(Ctx& c) {
     const float4* pt = reinterpret_cast<const float4*>(p.att_part + ((size_t)rb * ks * ATT_ROWS + rl) * 256 + 128 * half) + c.lane;
     float mx = -INFINITY, L = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s0 = 0; s0 < ks; s0 += 8) {
-      float2 sv[8];
-      float4 pv[8];
+    for (int s0 = 0; s0 < ks; s0 += MRG_BATCH) {
+      float2 sv[MRG_BATCH];
+      float4 pv[MRG_BATCH];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < MRG_BATCH; ++i) {
         const bool in = s0 + i < ks;
         sv[i] = in ? __ldcg(st + (size_t)(s0 + i) * ATT_ROWS) : make_float2(-INFINITY, 0.f);
         pv[i] = in ? __ldcg(pt + (size_t)(s0 + i) * ATT_ROWS * 64) : make_float4(0.f, 0.f, 0.f, 0.f);
       }
       float bm = mx;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) bm = fmaxf(bm, sv[i].x);
+      for (int i = 0; i < MRG_BATCH; ++i) bm = fmaxf(bm, sv[i].x);
       // rescale what has been accumulated so far to the new maximum (first batch: nothing accumulated, factor irrelevant)
       const float resc = (mx == -INFINITY) ? 0.f : exp2f(mx - bm);
       L *= resc; acc.x *= resc; acc.y *= resc; acc.z *= resc; acc.w *= resc;
       mx = bm;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < MRG_BATCH; ++i) {
         const float w = sv[i].x == -INFINITY ? 0.f : exp2f(sv[i].x - mx);
         L += w * sv[i].y;
         acc.x += w * pv[i].x; acc.y += w * pv[i].y; acc.z += w * pv[i].z; acc.w += w * pv[i].w;
@@ -1008,6 +1013,9 @@ __device__ __forceinline__ void activation_producer_loop(Ctx& c) {
     const unsigned int target = (unsigned int)phase * (unsigned int)p.G;
     const uint64_t t0 = globaltimer_ns();
     unsigned int spins = 0, v;
+    // one load in flight per CTA: sampling the counter more often (three relaxed loads in flight and an acquire fence
+    // behind the one that saw the target) made every barrier 0.5 us slower, the L2 slice that holds the counter being
+    // shared with the 148 arrivals
     for (;;) {
       asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.bar_ctr) : "memory");
       if (v >= target) break;
@@ -1054,10 +1062,11 @@ __device__ __forceinline__ void activation_producer_loop(Ctx& c) {
         const int rb = c.cta / p.att_ks, sp = c.cta - rb * p.att_ks;
         const int row_k = l * p.T + sp * p.att_kps;
         const uint32_t kv_tile = (uint32_t)p.att_kps * 128;
-        mbar_expect_tx(c.att_full, 4 * 4096 + 8 * kv_tile);
-        tma_load_3d(c.sbase, &p.tm_k, c.att_full, 0, row_k, 0, pol);               // the four 64-dim blocks in one copy each
-        tma_load_3d(c.sbase + ATT_V_OFF, &p.tm_v, c.att_full, 0, row_k, 0, pol);
-        tma_load_3d(c.sbase + ATT_Q_OFF, &p.tm_q, c.att_full, 0, rb * ATT_ROWS, 0, pol);
+        mbar_expect_tx(c.att_full, 4 * 4096 + 4 * kv_tile);
+        mbar_expect_tx(c.att_full_v, 4 * kv_tile);
+        tma_load_3d(c.sbase + ATT_Q_OFF, &p.tm_q, c.att_full, 0, rb * ATT_ROWS, 0, pol);   // the four 64-dim blocks in one copy each
+        tma_load_3d(c.sbase, &p.tm_k, c.att_full, 0, row_k, 0, pol);
+        tma_load_3d(c.sbase + ATT_V_OFF, &p.tm_v, c.att_full_v, 0, row_k, 0, pol);         // needed only after the softmax
         ++att_n;
       }
       begin_phase();                                // merge: reads global memory directly
@@ -1077,7 +1086,7 @@ __device__ __forceinline__ void activation_producer_loop(Ctx& c) {
     for (unsigned int i = (g > 4 ? g - 4 : 0); i < g; ++i)
       for (int tries = 0; tries < 20000 && !mbar_try_wait(c.a_full + 8 * (i & 3u), (i >> 2) & 1u); ++tries) __nanosleep(50);
     if (att_n > 0)
-      for (int tries = 0; tries < 20000 && !mbar_try_wait(c.att_full, (att_n - 1) & 1u); ++tries) __nanosleep(50);
+      for (int tries = 0; tries < 20000 && !(mbar_try_wait(c.att_full, (att_n - 1) & 1u) && mbar_try_wait(c.att_full_v, (att_n - 1) & 1u)); ++tries) __nanosleep(50);
   }
 }
 
@@ -1096,6 +1105,7 @@ __global__ void __launch_bounds__(THREADS, 1) expert_persistent_kernel(const __g
   c.a_full = c.w_empty + 8 * NSLOT;
   c.a_empty = c.a_full + 8 * N_ASTAGE;
   c.att_full = c.a_empty + 8 * N_ASTAGE;
+  c.att_full_v = c.att_full + 8;
   c.go_count = reinterpret_cast<volatile int*>(persist + 256);
   c.s_abort = reinterpret_cast<volatile int*>(persist + 260);
   c.fs = reinterpret_cast<float*>(persist + 512);
@@ -1125,6 +1135,7 @@ __global__ void __launch_bounds__(THREADS, 1) expert_persistent_kernel(const __g
       mbar_init(c.a_empty + 8 * s, 8);
     }
     mbar_init(c.att_full, 1);
+    mbar_init(c.att_full_v, 1);
     *c.go_count = 0;
     *c.s_abort = 0;
     mbar_fence_init();
@@ -1194,7 +1205,7 @@ __global__ void __launch_bounds__(THREADS, 1) expert_persistent_kernel(const __g
             next_scale = o ? p.style_ffn + sl * 3072
                            : ((l + 1 < p.nl) ? p.style_attn + (sl + 1) * 3072 : p.style_fin + (size_t)step * 3072);
           }
-          phase_resid(c, o ? 2048 : 4096, gate, next_scale);
+          phase_resid(c, o ? 2048 : 4096, gate, next_scale, !o && l + 1 == p.nl);
           break;
         }
         case K_GEGLU: phase_geglu(c, step, l); break;
