@@ -109,6 +109,31 @@ int vla_forward(vla_handle h, void* stream);
  * stage 1 and stage 2.  No counterpart in the reference (single GPU, one graph: pi0_infer.py:1232-1236). */
 int vla_forward_stages(vla_handle h, int stage_mask, void* stream);
 
+/* ---- multi-view latency mode with the exchange inside the graphs ------------------------------------------
+ * None of these has a counterpart in the reference, which runs on one GPU (pi0_infer.py:598-646 processes the views
+ * as one batch).  One process per GPU.  A "tower" is a single-view handle that runs stage 1 (vision) for one camera
+ * view; the "trunk" is the full handle that runs stages 2 and 4.  After the calls below, the last kernel of a tower's
+ * vision stage copies its (256, 2048) fp32 tile with plain peer stores over NVLink into a staging slot of the trunk's
+ * mailbox and raises a flag there; the first kernel of the trunk's prefix stage waits for the flags of all views,
+ * copies the slots into rows 256 v.. of "encoder_x" and acknowledges to every tower.  Forwards are counted on both
+ * sides, two staging slots alternate, and a tower does not overwrite a slot before the trunk has acknowledged the
+ * forward that used it, so towers may run ahead of the trunk by one forward and no more.  Every wait gives up after
+ * one second and raises the status word.  Every forward must run the vision stage of every tower and the prefix
+ * stage of the trunk exactly once (vla_forward_stages(tower, 1), vla_forward_stages(trunk, 2 | 4)).
+ *
+ * Set-up, after vla_finalize and before the first vla_forward_stages:
+ *   trunk process:  vla_link_trunk_create -> 64-byte CUDA IPC handle (for other processes) and the local pointer
+ *                   (for a tower in the same process, which cannot open its own process's handle)
+ *   tower process:  vla_link_tower_create -> the same pair for the tower's mailbox
+ *   exchange the handles (the Python wrapper uses torch.distributed.all_gather_object), vla_link_open them, then
+ *   vla_link_tower_connect(tower, trunk mailbox, view, n_views) and, per view, vla_link_trunk_connect(trunk, view,
+ *   that tower's mailbox).  Pointers returned by vla_link_open are closed by vla_destroy of the handle given. */
+int vla_link_trunk_create(vla_handle trunk, int n_views, unsigned char* ipc_handle_out, void** local_ptr_out);
+int vla_link_tower_create(vla_handle tower, unsigned char* ipc_handle_out, void** local_ptr_out);
+int vla_link_open(vla_handle h, const unsigned char* ipc_handle, void** ptr_out);
+int vla_link_tower_connect(vla_handle tower, void* trunk_mailbox, int view, int n_views);
+int vla_link_trunk_connect(vla_handle trunk, int view, void* tower_mailbox);
+
 /* Replaces Pi0Inference.forward / Pi05Inference.forward for a caller holding HOST memory
  * (pi0_infer.py:1356-1361): copies bf16 images/state/noise in, runs, copies the bf16 (batch,chunk,32)
  * actions out and synchronises.  `state` is ignored for Pi05 (may be NULL).  Returns VLA_ERR_DEVICE (and clears the

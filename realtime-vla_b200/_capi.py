@@ -60,6 +60,11 @@ EXPORTS = {
     "vla_buffer": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p), C.POINTER(C.c_size_t)]),
     "vla_forward": (C.c_int, [C.c_void_p, C.c_void_p]),
     "vla_forward_stages": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "vla_link_trunk_create": (C.c_int, [C.c_void_p, C.c_int, C.c_char_p, C.POINTER(C.c_void_p)]),
+    "vla_link_tower_create": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p)]),
+    "vla_link_open": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p)]),
+    "vla_link_tower_connect": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+    "vla_link_trunk_connect": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "vla_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "vla_status_word": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
     "vla_stats": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_size_t)]),

@@ -174,6 +174,29 @@ class Engine:
         stream = torch.cuda.current_stream(self.device).cuda_stream
         _capi.check(self.lib.vla_forward_stages(self.handle, int(mask), C.c_void_p(stream)), self.handle)
 
+    # ---- multi-view latency mode: mailboxes of the in-graph NVLink exchange (see include/vla_b200.h) ----
+    def link_create(self, n_views=0):
+        """Mailbox of a trunk (n_views > 0) or of a tower (0) -> (64-byte IPC handle, pointer valid in this process)."""
+        buf, ptr = C.create_string_buffer(64), C.c_void_p()
+        if n_views > 0:
+            rc = self.lib.vla_link_trunk_create(self.handle, int(n_views), buf, C.byref(ptr))
+        else:
+            rc = self.lib.vla_link_tower_create(self.handle, buf, C.byref(ptr))
+        _capi.check(rc, self.handle)
+        return buf.raw, ptr.value
+
+    def link_open(self, ipc_handle):
+        """Pointer to another process's mailbox (closed when this engine is destroyed)."""
+        ptr = C.c_void_p()
+        _capi.check(self.lib.vla_link_open(self.handle, C.create_string_buffer(ipc_handle, 64), C.byref(ptr)), self.handle)
+        return ptr.value
+
+    def link_tower_connect(self, trunk_mailbox, view, n_views):
+        _capi.check(self.lib.vla_link_tower_connect(self.handle, C.c_void_p(trunk_mailbox), int(view), int(n_views)), self.handle)
+
+    def link_trunk_connect(self, view, tower_mailbox):
+        _capi.check(self.lib.vla_link_trunk_connect(self.handle, int(view), C.c_void_p(tower_mailbox)), self.handle)
+
     def forward_host(self, images, state, noise, out):
         """Host-memory entry: contiguous bf16 CPU tensors in, actions written to `out` (bf16 CPU)."""
         _capi.check(self.lib.vla_forward_host(self.handle, C.c_void_p(images.data_ptr()),

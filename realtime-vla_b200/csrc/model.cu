@@ -25,6 +25,7 @@
 #include "elementwise.cuh"
 #include "expert_persistent.cuh"
 #include "gemm_sm100.cuh"
+#include "link.cuh"
 #include "preprocess.cuh"
 
 namespace {
@@ -540,6 +541,12 @@ struct vla_model {
   unsigned int* xp_sync = nullptr;
   unsigned long long* xp_trace = nullptr;
   xp::Params xp_params;
+
+  // multi-view latency mode over NVLink (link.cuh): this handle's mailbox and what it has opened of other processes
+  uint8_t* link_box = nullptr;
+  int link_views = 0;              // > 0: trunk mailbox for that many views; 0 with link_box set: tower mailbox
+  bool link_connected = false;
+  std::vector<void*> ipc_opened;
 
   struct Op { int stage; bool is_kernel; std::function<cudaError_t(cudaStream_t)> fn; };
   std::vector<Op> ops;
@@ -1493,6 +1500,108 @@ int vla_forward_stages(vla_handle m, int stage_mask, void* stream) {
   return VLA_OK;
 }
 
+// ---- multi-view latency mode: image tokens pushed over NVLink inside the captured graphs (link.cuh) -----------------
+namespace {
+void drop_stage_graphs(vla_model* m) {
+  for (auto& kv : m->stage_graphs) cudaGraphExecDestroy(kv.second);
+  m->stage_graphs.clear();
+}
+int link_export(vla_model* m, unsigned char* ipc_handle_out, void** local_ptr_out) {
+  if (ipc_handle_out) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the header promises 64 bytes");
+    cudaIpcMemHandle_t h;
+    CK(cudaIpcGetMemHandle(&h, m->link_box));
+    memcpy(ipc_handle_out, &h, sizeof h);
+  }
+  if (local_ptr_out) *local_ptr_out = m->link_box;
+  return VLA_OK;
+}
+}  // namespace
+
+int vla_link_trunk_create(vla_handle m, int n_views, unsigned char* ipc_handle_out, void** local_ptr_out) {
+  if (!m || !m->finalized) return m ? m->fail(VLA_ERR_STATE, "link before finalize") : VLA_ERR_STATE;
+  if (m->link_box) return m->fail(VLA_ERR_STATE, "this handle already has a mailbox");
+  if (m->B != 1 || n_views < 1 || n_views > lk::MAX_VIEWS || n_views != m->nv)
+    return m->fail(VLA_ERR_SHAPE, "the trunk of latency mode is a single-observation handle with one tower per view (%d views)", m->nv);
+  cudaSetDevice(m->cfg.device);
+  const size_t bytes = lk::TRUNK_STAGING_OFF + (size_t)2 * n_views * lk::TILE_FLOATS * sizeof(float);
+  if (!m->dalloc(&m->link_box, bytes)) return m->fail(VLA_ERR_CUDA, "mailbox allocation failed");
+  m->link_views = n_views;
+  return link_export(m, ipc_handle_out, local_ptr_out);
+}
+
+int vla_link_tower_create(vla_handle m, unsigned char* ipc_handle_out, void** local_ptr_out) {
+  if (!m || !m->finalized) return m ? m->fail(VLA_ERR_STATE, "link before finalize") : VLA_ERR_STATE;
+  if (m->link_box) return m->fail(VLA_ERR_STATE, "this handle already has a mailbox");
+  if (m->B != 1 || m->nv != 1) return m->fail(VLA_ERR_SHAPE, "a tower of latency mode is a single-observation, single-view handle");
+  cudaSetDevice(m->cfg.device);
+  if (!m->dalloc(&m->link_box, lk::TOWER_BOX_BYTES)) return m->fail(VLA_ERR_CUDA, "mailbox allocation failed");
+  m->link_views = 0;
+  return link_export(m, ipc_handle_out, local_ptr_out);
+}
+
+int vla_link_open(vla_handle m, const unsigned char* ipc_handle, void** ptr_out) {
+  if (!m || !ipc_handle || !ptr_out) return VLA_ERR_STATE;
+  cudaSetDevice(m->cfg.device);
+  cudaIpcMemHandle_t h;
+  memcpy(&h, ipc_handle, sizeof h);
+  void* p = nullptr;
+  CK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  m->ipc_opened.push_back(p);
+  *ptr_out = p;
+  return VLA_OK;
+}
+
+int vla_link_tower_connect(vla_handle m, void* trunk_mailbox, int view, int n_views) {
+  if (!m || !m->link_box || m->link_views != 0 || !trunk_mailbox) return m ? m->fail(VLA_ERR_STATE, "not a tower with a mailbox") : VLA_ERR_STATE;
+  if (m->link_connected) return m->fail(VLA_ERR_STATE, "tower already connected");
+  if (view < 0 || view >= n_views || n_views > lk::MAX_VIEWS) return m->fail(VLA_ERR_SHAPE, "view %d of %d", view, n_views);
+  cudaSetDevice(m->cfg.device);
+  const float4* tile = reinterpret_cast<const float4*>(m->encoder_x);
+  float4* staging = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(trunk_mailbox) + lk::TRUNK_STAGING_OFF);
+  unsigned int* flags = reinterpret_cast<unsigned int*>(trunk_mailbox);
+  unsigned int* box = reinterpret_cast<unsigned int*>(m->link_box);
+  int* status = m->d_status;
+  const int grid = m->sm_count;
+  // last node of the vision stage
+  auto it = m->ops.begin();
+  for (auto j = m->ops.begin(); j != m->ops.end(); ++j)
+    if (j->stage == 0) it = j + 1;
+  m->ops.insert(it, {0, true, [=](cudaStream_t st) {
+                       lk::push_kernel<<<grid, 256, 0, st>>>(tile, staging, flags, box, view, n_views, status);
+                       return cudaGetLastError();
+                     }});
+  m->n_kernels++;
+  m->link_connected = true;
+  drop_stage_graphs(m);
+  return VLA_OK;
+}
+
+int vla_link_trunk_connect(vla_handle m, int view, void* tower_mailbox) {
+  if (!m || !m->link_box || m->link_views == 0 || !tower_mailbox) return m ? m->fail(VLA_ERR_STATE, "not a trunk with a mailbox") : VLA_ERR_STATE;
+  if (view < 0 || view >= m->link_views) return m->fail(VLA_ERR_SHAPE, "view %d of %d", view, m->link_views);
+  cudaSetDevice(m->cfg.device);
+  unsigned int* ack = reinterpret_cast<unsigned int*>(tower_mailbox) + lk::TOWER_ACK;
+  CK(cudaMemcpy(m->link_box + lk::TRUNK_ACK_OFF + view * sizeof(unsigned int*), &ack, sizeof ack, cudaMemcpyHostToDevice));
+  if (!m->link_connected) {
+    float4* x = reinterpret_cast<float4*>(m->encoder_x);
+    unsigned int* box = reinterpret_cast<unsigned int*>(m->link_box);
+    const int n_views = m->link_views, grid = m->sm_count;
+    int* status = m->d_status;
+    // first node of the prefix stage
+    auto it = m->ops.begin();
+    while (it != m->ops.end() && it->stage < 1) ++it;
+    m->ops.insert(it, {1, true, [=](cudaStream_t st) {
+                         lk::wait_kernel<<<grid, 256, 0, st>>>(x, box, n_views, status);
+                         return cudaGetLastError();
+                       }});
+    m->n_kernels++;
+    m->link_connected = true;
+    drop_stage_graphs(m);
+  }
+  return VLA_OK;
+}
+
 int vla_forward_host(vla_handle m, const void* images, const void* state, const void* noise, void* actions_out) {
   if (!m || !m->finalized) return m ? m->fail(VLA_ERR_STATE, "forward before finalize") : VLA_ERR_STATE;
   if (!images || !noise || !actions_out || (!m->pi05 && !state)) return m->fail(VLA_ERR_STATE, "null input");
@@ -1726,6 +1835,7 @@ int vla_destroy(vla_handle m) {
   if (m->own_stream) cudaStreamDestroy(m->own_stream);
   if (m->h_scalars) cudaFreeHost(m->h_scalars);
   if (m->h_status) cudaFreeHost(m->h_status);
+  for (void* p : m->ipc_opened) cudaIpcCloseMemHandle(p);
   for (void* p : m->allocs) cudaFree(p);
   delete m;
   return VLA_OK;
