@@ -482,15 +482,16 @@ def run_reference(args, wl, rank, world):
 
 
 def run_latency_mode(args, wl, rank, world, local, device, dist):
-    """Multi-view latency mode: rank v < num_views runs the SigLIP tower of view v, the projected tiles are
-    gathered over NCCL into rank 0, which runs the prefix prefill and the action expert."""
+    """Multi-view latency mode: rank v < num_views runs the SigLIP tower of view v, the projected tiles reach rank 0
+    either inside the captured graphs (peer stores over NVLink, --exchange fused) or through an NCCL gather between
+    two graph launches (--exchange nccl); rank 0 runs the prefix prefill and the action expert."""
     import multi_gpu as M
     nv = wl["num_views"]
     if world < nv or wl["model"] != "pi0":
         raise SystemExit("--mode latency needs a Pi0 workload and one rank per view (%d views, %d ranks)" % (nv, world))
     ck = fast_checkpoint("pi0", wl["prompt_len"], wl["seed"], device)
     Tower, Trunk = M.gpu_factories(ck, nv, wl["chunk"], device=local, flags=args.flags)
-    runner = M.MultiViewLatencyPi0(nv, Tower, Trunk)
+    runner = (M.FusedLatencyPi0 if args.exchange == "fused" else M.MultiViewLatencyPi0)(nv, Tower, Trunk)
     images, state, noise = inputs(wl, device)
     host_args = [t.cpu().pin_memory() for t in (images, state, noise)]
     step = lambda: runner.forward(images, state, noise)
@@ -542,9 +543,10 @@ def run_latency_mode(args, wl, rank, world, local, device, dist):
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": args.workload, **{k: wl[k] for k in ("model", "num_views", "prompt_len", "chunk")},
                            "euler_steps": 10, "batch_per_gpu": 1,
-                           "parallelism": "latency mode: %d SigLIP towers on %d GPUs, NCCL gather of the projected tiles, prefix + expert on rank 0" % (nv, nv)},
+                           "parallelism": "latency mode: %d SigLIP towers on %d GPUs, %s, prefix + expert on rank 0" %
+                                          (nv, nv, "tiles pushed over NVLink inside the graphs" if args.exchange == "fused" else "NCCL gather of the projected tiles")},
                 "latency_ms": {"p50": round(percentile(lat, 0.5), 4), "p99": round(percentile(lat, 0.99), 4),
-                               "note": "rank 0, device events around tower + gather + prefix + expert"},
+                               "note": "rank 0, device events around tower + exchange + prefix + expert"},
                 "e2e": {"value": round(args.steps / (e2e_ms * 1e-3), 3), "unit": "obs/s",
                         "h2d_bytes_per_step": sum(x.numel() * 2 for x in host_args), "d2h_bytes_per_step": wl["chunk"] * 32 * 2,
                         "ms_per_step": round(e2e_ms / args.steps, 4)},
@@ -568,6 +570,8 @@ def main():
     ap.add_argument("--mode", default="replicas", choices=["replicas", "latency"],
                     help="replicas: every rank runs whole forwards (default); latency: one observation, one SigLIP tower "
                          "per rank + gather (needs at least num_views ranks)")
+    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
+                    help="latency mode: image tokens pushed over NVLink inside the graphs, or an NCCL gather between two graph launches")
     ap.add_argument("--flags", type=int, default=0, help="vla_config.flags: 1 = no programmatic dependent launch, 2 = no CUDA graph")
     ap.add_argument("--microbench", nargs="?", const="geglu", default=None, choices=["geglu", "expert_down", "expert_attention", "siglip_attention", "preprocess"],
                     help="time one kernel alone and print its roofline object: geglu = the dominant kernel of the workload "

@@ -600,6 +600,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       if (lane == 0) bulk_wait_all();
       __syncwarp();
     } else if (is_epi && acc_ok) {
+      const bool vt_by_keys = p.epi.kind == EPI_QKV && p.epi.vt != nullptr && feat0 >= 2304;
 #pragma unroll 1
       for (int pass = 0; pass < n_pass; ++pass) {
         for (int c0 = 32 * half; c0 < umma_n; c0 += 64) {
@@ -615,6 +616,30 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
             }
           }
           const int n_valid = min(32, p.n_tok - (tok0 + c0));
+          if (vt_by_keys) {
+            // Value tile with a transposed cache: a thread owns one feature, so writing V^T[feature][key] from the
+            // accumulator layout puts the 32 lanes of a store on 32 different rows (32 partial sectors per
+            // instruction; the value tiles were the long pole of the batched QKV launch).  The 32 x 32 block goes
+            // through this warp's slice of the idle pipeline stages instead and is written with lanes along the keys.
+            bf16* tsp = reinterpret_cast<bf16*>(smem + (warp - 2) * 8192);
+            const EpiThread& th = pass ? th2 : th_first;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) tsp[j * 34 + lane] = __float2bfloat16(__uint_as_float(v[j]) + th.bias);
+            __syncwarp();
+            const int t = tok0 + c0 + lane;
+            if (t < p.n_tok) {
+              const int obs = t / p.epi.rows_per_obs, lrow = t - obs * p.epi.rows_per_obs;
+              bf16* dst = p.epi.vt + ((size_t)obs * 256 + (feat0 + pass * 128 - 2304 + q * 32)) * p.epi.vt_ld + p.epi.kv_row_off + lrow;
+#pragma unroll
+              for (int f = 0; f < 32; ++f) dst[(size_t)f * p.epi.vt_ld] = tsp[lane * 34 + f];
+            }
+            __syncwarp();
+            GemmEpi e2 = p.epi;
+            e2.vt = nullptr;   // the row-major value cache is written by the generic path
+            gemm_epilogue_cols<32>(e2, th, tok0 + c0, 1, n_valid, reinterpret_cast<const float*>(v),
+                                   reinterpret_cast<const float*>(m256 ? v : v2));
+            continue;
+          }
           gemm_epilogue_cols<32>(p.epi, pass ? th2 : th_first, tok0 + c0, 1, n_valid, reinterpret_cast<const float*>(v),
                                  reinterpret_cast<const float*>(m256 ? v : v2));
         }
