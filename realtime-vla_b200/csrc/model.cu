@@ -292,7 +292,7 @@ cudaError_t launch_gemm(const GemmOp& op, cudaStream_t st, bool pdl) {
 // w / w2: repacked weights [n_feat_pad, Kp]; x: activations [tokens, K] with pitch ldx.
 bool build_gemm(GemmOp* op, const bf16* w, const bf16* w2, int n_feat, int n_feat_pad, int Kp, const bf16* x, int tokens,
                 int Kx, int ldx, const GemmEpi& epi, int* status, int sm_count, int force_bn, int force_split,
-                std::string* err, int m256_mode = 0, int force_tok_tile = 0, int cg2_mode = 0) {
+                std::string* err, int m256_mode = 0, int force_tok_tile = 0, int cg2_mode = 0, bool fill_wave = true) {
   memset(op, 0, sizeof *op);
   op->dual = w2 != nullptr;
   if (Kp % 64 || n_feat_pad % 128) { *err = "repacked weight must be padded to 128 features x 64 K"; return false; }
@@ -334,7 +334,9 @@ bool build_gemm(GemmOp* op, const bf16* w, const bf16* w2, int n_feat, int n_fea
   // the wave is full: the K loop of a CTA is bound by its MMAs (2 clk per token and 16-wide K step) or by the bytes it
   // pulls from L2, both of which shrink with the tile (SigLIP QKV at 768 tokens: 27 feature tiles x 3 token tiles of
   // 256 = 81 CTAs become 27 x 5 tiles of 160 = 135 CTAs).
-  if (tokens >= 192 && !m256) {
+  // (fill_wave = false keeps the coarse tiles: more CTAs also mean more split-K scratch, which the allocation-free entry
+  // point takes from a fixed array)
+  if (fill_wave && tokens >= 192 && !m256) {
     const int per_tok_tile = (cg2 ? 2 * ((feat_tiles + 1) / 2) : feat_tiles) * split;
     const int resident = split * (cg2 ? 2 : 1) >= 4 ? 128 : sm_count;
     int n_tiles = (tokens + tok_tile - 1) / tok_tile;
@@ -2078,7 +2080,7 @@ int vla_op_gemm_noalloc(const vla_gemm_noalloc_desc* d, void* stream) {
   int split = d->split;
   for (;;) {
     if (!build_gemm(&op, reinterpret_cast<const bf16*>(d->w_nk), nullptr, d->N, d->n_pad, d->k_pad,
-                    reinterpret_cast<const bf16*>(d->x), d->tokens, d->K, d->K, e, nd->status, sms, 0, split, &err, -1, 0, -1)) {
+                    reinterpret_cast<const bf16*>(d->x), d->tokens, d->K, d->K, e, nd->status, sms, 0, split, &err, -1, 0, -1, false)) {
       g_last_error = "vla_op_gemm_noalloc: " + err;
       return VLA_ERR_SHAPE;
     }
