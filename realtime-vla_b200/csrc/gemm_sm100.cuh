@@ -671,12 +671,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     if (threadIdx.x == 64) GEMM_TRACE(8);
     KTRACE_T(15, 64);
     if (is_epi) {
-      // this CTA owns columns rank, rank+split, ...; the two warps of a quarter alternate groups of 4 of them
+      // this CTA owns columns rank, rank+split, ...; the two warps of a quarter alternate groups of G of them
+      // (all partial-tile loads of a group are in flight together, then the residual loads, then the stores: the loop is
+      // a chain of L2 round trips, so a group of 8 columns halves its length against 4)
+      constexpr int G = 8;
       const int n_owned = n_cols > rank ? (n_cols - rank + split - 1) / split : 0;
-      for (int i0 = 4 * half; i0 < n_owned; i0 += 8) {
-        float s1[4], s2[4];
+      for (int i0 = G * half; i0 < n_owned; i0 += 2 * G) {
+        float s1[G], s2[G];
 #pragma unroll
-        for (int ci = 0; ci < 4; ++ci) {
+        for (int ci = 0; ci < G; ++ci) {
           const int c = rank + (i0 + ci) * split;
           float a[8], b[8];
 #pragma unroll
@@ -696,12 +699,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
             s2[ci] *= f;
           }
         }
-        const int n_valid = min(4, n_owned - i0);
+        const int n_valid = min(G, n_owned - i0);
         if (m256) {
-          gemm_epilogue_cols<4>(p.epi, th_first, tok0 + rank + i0 * split, split, n_valid, s1, s1);
-          gemm_epilogue_cols<4>(p.epi, th2, tok0 + rank + i0 * split, split, n_valid, s2, s2);
+          gemm_epilogue_cols<G>(p.epi, th_first, tok0 + rank + i0 * split, split, n_valid, s1, s1);
+          gemm_epilogue_cols<G>(p.epi, th2, tok0 + rank + i0 * split, split, n_valid, s2, s2);
         } else {
-          gemm_epilogue_cols<4>(p.epi, th_first, tok0 + rank + i0 * split, split, n_valid, s1, s2);
+          gemm_epilogue_cols<G>(p.epi, th_first, tok0 + rank + i0 * split, split, n_valid, s1, s2);
         }
       }
     }
