@@ -203,8 +203,27 @@ int pick_split(int units, int k_blocks, int sm_count) {
 // A third shape, cg2, runs neighbouring feature tiles as tcgen05 CTA pairs that share the activation tile, each CTA
 // loading half of it (16 KB + 64 B per token per K block and CTA): same CTA count and exchange as the plain shape.
 // cg2_mode: 0 = let the model choose, 1 = force, -1 = never.
+// Tokens per CTA along grid.y for `tokens` rows in tiles of at most b: the tiles are evened out (788 tokens = 4 x 224
+// rather than 3 x 256 + 20), and a launch that fits the SMs in one wave with room to spare takes more, smaller tiles
+// (multiples of 32) until the wave is full: the K loop of a CTA is bound by its MMAs (2 clk per token and 16-wide K
+// step) or by the bytes it pulls from L2, both of which shrink with the tile (SigLIP QKV at 768 tokens: 27 feature
+// tiles x 3 token tiles of 256 = 81 CTAs become 27 x 5 tiles of 160 = 135 CTAs).  ctas_per_tok_tile = CTAs per
+// token tile (feature tiles x K split).
+int even_tok_tile(int tokens, int b, int ctas_per_tok_tile, int resident, bool fill_wave) {
+  int tok_tile = b;
+  int n_tiles = (tokens + b - 1) / b;
+  if (tokens > b) tok_tile = std::min(b, ((tokens + n_tiles - 1) / n_tiles + 31) / 32 * 32);
+  if (fill_wave && tokens >= 192 && ctas_per_tok_tile * n_tiles <= resident) {
+    n_tiles = std::min(std::max(n_tiles, resident / ctas_per_tok_tile), (tokens + 31) / 32);
+    tok_tile = std::min(tok_tile, ((tokens + n_tiles - 1) / n_tiles + 31) / 32 * 32);
+  }
+  return tok_tile;
+}
+
+// qkv: the launch has the QKV epilogue, whose split-K form (rotary table loads and cache-row arithmetic per owned column,
+// scattered stores of the transposed values) measured 5 us slower than the unsplit tile-store form at 256 tokens.
 void pick_tiling(int tokens, int feat_tiles, int k_blocks, bool dual, int sm_count, int* bn, int* split, int* m256,
-                 int m256_mode = 0, int* cg2 = nullptr, int cg2_mode = 0) {
+                 int m256_mode = 0, int* cg2 = nullptr, int cg2_mode = 0, bool qkv = false) {
   *m256 = 0;
   if (cg2) *cg2 = 0;
   if (tokens <= 128 && m256_mode <= 0) {
@@ -238,12 +257,15 @@ void pick_tiling(int tokens, int feat_tiles, int k_blocks, bool dual, int sm_cou
         // took 72 us paired with K split 4 against 68 us unpaired, 17 024 tokens 870 us against 1 076 us)
         if (pair && m256_mode == 0 && (s > 1 || ctas < 2LL * sm_count)) continue;
         const int kb = (k_blocks + s - 1) / s;
+        // (costing an unsplit launch with the smaller token tiles it ends up with, see even_tok_tile, chose unsplit
+        // long-K launches that measure slower: SigLIP down projection at 512 tokens 25.6 against 18.6 us; configuration 3
+        // 11.65 -> 12.18 ms.  The tile shape is therefore chosen for the coarse tiles and refined afterwards.)
         const double load = kb * (16384.0 * accs + (two ? 64.0 : 128.0) * b) / 64.0;
         const double mma = kb * 2.0 * b * accs;
         const double epi = 22.0 * (b / 2) * accs;
         // partial tile through L2 + cluster barrier; measured cheaper than twice the 128-token figure for a 4-way
         // split of 256-token tiles (SigLIP down projection at 768 tokens: 22.7 us against 25.9 us for 128 x 2)
-        const double exch = s > 1 ? 5000.0 * (b == 256 ? (s == 4 ? 1.5 : 2.0) : 1.0) * accs : 0.0;
+        const double exch = s > 1 ? 5000.0 * (b == 256 ? (s == 4 ? 1.5 : 2.0) : 1.0) * accs + (qkv ? 8000.0 : 0.0) : 0.0;
         const double cta = (load > mma ? load : mma) + epi + exch;
         // clusters are scheduled whole within a GPC: 144 CTAs in clusters of 4 measured like two waves
         // (512 x 4304 x 1152: 29 us against 25 us for 72 CTAs), so 4- and 8-CTA clusters count 128 resident CTAs
@@ -299,7 +321,8 @@ bool build_gemm(GemmOp* op, const bf16* w, const bf16* w2, int n_feat, int n_fea
   int feat_tiles = n_feat_pad / 128;
   const int kb = Kp / 64;
   int bn, split, m256, cg2;
-  pick_tiling(tokens, feat_tiles, kb, op->dual, sm_count, &bn, &split, &m256, m256_mode, &cg2, cg2_mode);
+  pick_tiling(tokens, feat_tiles, kb, op->dual, sm_count, &bn, &split, &m256, m256_mode, &cg2, cg2_mode,
+              epi.kind == EPI_QKV && epi.rows_per_obs >= tokens);
   if (force_bn > 0) {
     bn = force_bn;
     if (bn != 64 && bn != 128 && bn != 256) { *err = "token tile must be 64, 128 or 256"; return false; }
@@ -323,28 +346,10 @@ bool build_gemm(GemmOp* op, const bf16* w, const bf16* w2, int n_feat, int n_fea
   }
   op->p.m256 = m256;
   op->bn = bn;
-  // Even out the token tiles: same number of tiles, each a multiple of 32 tokens (the epilogue's store blocks),
-  // so that no CTA streams the whole weight panel for a few leftover tokens.
-  int tok_tile = bn;
-  if (tokens > bn) {
-    const int n_tiles = (tokens + bn - 1) / bn;
-    tok_tile = std::min(bn, (((tokens + n_tiles - 1) / n_tiles) + 31) / 32 * 32);
-  }
-  // A launch that fits the SMs in one wave with room to spare takes more, smaller token tiles (multiples of 32) until
-  // the wave is full: the K loop of a CTA is bound by its MMAs (2 clk per token and 16-wide K step) or by the bytes it
-  // pulls from L2, both of which shrink with the tile (SigLIP QKV at 768 tokens: 27 feature tiles x 3 token tiles of
-  // 256 = 81 CTAs become 27 x 5 tiles of 160 = 135 CTAs).
-  // (fill_wave = false keeps the coarse tiles: more CTAs also mean more split-K scratch, which the allocation-free entry
-  // point takes from a fixed array)
-  if (fill_wave && tokens >= 192 && !m256) {
-    const int per_tok_tile = (cg2 ? 2 * ((feat_tiles + 1) / 2) : feat_tiles) * split;
-    const int resident = split * (cg2 ? 2 : 1) >= 4 ? 128 : sm_count;
-    int n_tiles = (tokens + tok_tile - 1) / tok_tile;
-    if (per_tok_tile * n_tiles <= resident) {
-      n_tiles = std::min(std::max(n_tiles, resident / per_tok_tile), (tokens + 31) / 32);
-      tok_tile = std::min(tok_tile, ((tokens + n_tiles - 1) / n_tiles + 31) / 32 * 32);
-    }
-  }
+  // Even out the token tiles and fill the wave (fill_wave = false keeps the coarse tiles: more CTAs also mean more
+  // split-K scratch, which the allocation-free entry point takes from a fixed array).
+  int tok_tile = even_tok_tile(tokens, bn, (cg2 ? 2 * ((feat_tiles + 1) / 2) : feat_tiles) * split,
+                               split * (cg2 ? 2 : 1) >= 4 ? 128 : sm_count, fill_wave && !m256);
   if (force_tok_tile > 0) {
     if (force_tok_tile % 32 || force_tok_tile > bn) { *err = "token tile stride must be a multiple of 32 and <= bn"; return false; }
     tok_tile = force_tok_tile;
