@@ -1083,8 +1083,11 @@ void plan_decoder(Plan& pl) {
       // The RMS norms are folded into the GEMMs (f * (x @ W)); only the first layer of a step normalises
       // explicitly, because its input comes from the action MLP.  Pi05 (adaRMS): the producer's bf16 mirror holds
       // x * (1 + scale) of the norm that consumes it and the consumer adds the precomputed shift @ W as a bias.
-      const bool fold = true;
-      const bool explicit_norm = l == 0;
+      // Batched forwards do not fold: the producer side of the fold (bf16 mirror + per-token sums of squares) keeps the
+      // residual GEMMs on the per-column epilogue, which at 1632 tokens costs more (39 us per launch) than two norm
+      // launches and the tile-store epilogue (in-place fp32 reduce-add through TMA) together.
+      const bool fold = B == 1;
+      const bool explicit_norm = !fold || l == 0;
       const size_t sl = (size_t)step * m->nl + l;
       if (explicit_norm) pl.norm(m->decoder_x, m->decoder_xn, Ns, 1024, pi05 ? NORM_ADARMS : NORM_RMS, st_attn, nullptr);
       GemmEpi e = pl.epi0();
@@ -1111,18 +1114,19 @@ void plan_decoder(Plan& pl) {
       e.kind = EPI_RESID; e.outf = m->decoder_x; e.ld_outf = 1024; e.res_in = m->decoder_x; e.ld_res = 1024;
       e.gate = pi05 ? st_attn + 2048 : nullptr;
       if (fold) { e.mirror = m->decoder_xb; e.ld_mirror = 1024; e.ssq_out = m->decoder_ssq; e.ssq_ld = Ns; }
-      if (pi05) e.mirror_scale = st_ffn;   // scale third of the pre-MLP norm's style row
+      if (pi05 && fold) e.mirror_scale = st_ffn;   // scale third of the pre-MLP norm's style row
       pl.gemm("decoder_attn_o_w", nullptr, l, m->decoder_attn, Ns, 2048, 2048, e);
+      if (!fold) pl.norm(m->decoder_x, m->decoder_xn, Ns, 1024, pi05 ? NORM_ADARMS : NORM_RMS, st_ffn, nullptr);
       e = pl.epi0();
       e.kind = EPI_BF16; e.act = ACT_GEGLU; e.out = m->decoder_hidden; e.ld_out = 4096;
       if (fold) { e.ssq_in = m->decoder_ssq; e.ssq_ld = Ns; e.ssq_slots = 32; e.ssq_inv_d = 1.0f / 1024.0f; }
-      if (pi05) { e.bias = m->sw_gate + sl * 4096; e.bias2 = m->sw_up + sl * 4096; }
+      if (pi05 && fold) { e.bias = m->sw_gate + sl * 4096; e.bias2 = m->sw_up + sl * 4096; }
       pl.gemm("decoder_ffn_gate_w", "decoder_ffn_up_w", l, fold ? m->decoder_xb : m->decoder_xn, Ns, 1024, 1024, e);
       e = pl.epi0();
       e.kind = EPI_RESID; e.outf = m->decoder_x; e.ld_outf = 1024; e.res_in = m->decoder_x; e.ld_res = 1024;
       e.gate = pi05 ? st_ffn + 2048 : nullptr;
       if (fold) { e.mirror = m->decoder_xb; e.ld_mirror = 1024; e.ssq_out = m->decoder_ssq; e.ssq_ld = Ns; }
-      if (pi05 && l + 1 < m->nl) e.mirror_scale = st_attn + 3072;   // pre-attention norm of the next layer, same step
+      if (pi05 && fold && l + 1 < m->nl) e.mirror_scale = st_attn + 3072;   // pre-attention norm of the next layer, same step
       pl.gemm("decoder_ffn_down_w", nullptr, l, m->decoder_hidden, Ns, 4096, 4096, e);
     }
     // Euler update: noise += norm(x_action) @ W_out + b_out   (pi0_infer.py:1224-1230, pi05_infer.py:511-523)
