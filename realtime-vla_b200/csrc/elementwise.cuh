@@ -176,3 +176,55 @@ __global__ void copy_rows_kernel(const float* __restrict__ src, float* __restric
   const int b = idx / width, c = idx - b * width;
   dst[((size_t)b * dst_stride_rows + dst_off_rows) * width + c] = src[(size_t)b * width + c];
 }
+
+// Batched forwards: rotary embedding and K/V-cache append as a pass of their own over the bf16 output [tokens, 2560] of
+// a plain QKV GEMM (what the reference does with its fused rope/split kernels, pi0_infer.py:777-810).  Inside the GEMM
+// this work sits in a per-column epilogue, because 51 suffix rows per observation break every 32-token store block
+// across cache rows of two observations; as its own kernel it is one coalesced read and write.
+// One block = 32 consecutive tokens (blockIdx.x) x 512 features (blockIdx.y = 0..4).  Token t belongs to observation t / rows_per_obs, local row r = t % rows_per_obs,
+// position r + pos_off + *pos_base, cache row obs * kv_obs_stride + kv_row_off + r.  Features [0, 2048) -> q (rotated
+// in adjacent pairs), [2048, 2304) -> key cache (rotated), [2304, 2560) -> value cache and, through a transpose in
+// shared memory so that the lanes of a store run along the keys, the transposed value cache vt[obs][256][vt_ld].
+__global__ void __launch_bounds__(256) qkv_rope_split_kernel(const bf16* __restrict__ qkv, int n_tok, bf16* __restrict__ q,
+                                                             bf16* __restrict__ kc, bf16* __restrict__ vc, bf16* __restrict__ vt,
+                                                             int vt_ld, const float* __restrict__ rope_cos,
+                                                             const float* __restrict__ rope_sin, int pos_off,
+                                                             const int* __restrict__ pos_base, int rows_per_obs,
+                                                             int kv_obs_stride, int kv_row_off) {
+  __shared__ bf16 vtile[32][258];   // [token][dim], rows padded so that the transposed reads hit distinct banks
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int t0 = blockIdx.x * 32;
+  const int pb = pos_base ? *pos_base : 0;
+  for (int i = threadIdx.x; i < 32 * 256; i += 256) {   // pairs of adjacent features
+    const int tl = i >> 8, n = 512 * blockIdx.y + 2 * (i & 255), t = t0 + tl;
+    if (t >= n_tok) continue;
+    const int obs = t / rows_per_obs, r = t - obs * rows_per_obs;
+    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(qkv + (size_t)t * 2560 + n);
+    float v0 = __low2float(x), v1 = __high2float(x);
+    if (n < 2304) {
+      const int pos = r + pos_off + pb, fi = (n & 255) >> 1;
+      const float c = rope_cos[pos * 128 + fi], sn = rope_sin[pos * 128 + fi];
+      const float a = v0 * c - v1 * sn, b = v1 * c + v0 * sn;
+      v0 = a; v1 = b;
+    }
+    const __nv_bfloat162 o = __floats2bfloat162_rn(v0, v1);
+    const size_t row = (size_t)obs * kv_obs_stride + kv_row_off + r;
+    if (n < 2048) *reinterpret_cast<__nv_bfloat162*>(q + (size_t)t * 2048 + n) = o;
+    else if (n < 2304) *reinterpret_cast<__nv_bfloat162*>(kc + row * 256 + (n - 2048)) = o;
+    else {
+      *reinterpret_cast<__nv_bfloat162*>(vc + row * 256 + (n - 2304)) = o;
+      *reinterpret_cast<__nv_bfloat162*>(&vtile[tl][n - 2304]) = o;
+    }
+  }
+  if (!vt || blockIdx.y != 4) return;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = t0 + lane;
+  if (t < n_tok) {
+    const int obs = t / rows_per_obs, r = t - obs * rows_per_obs;
+    bf16* dst = vt + ((size_t)obs * 256 + warp * 32) * vt_ld + kv_row_off + r;
+#pragma unroll 8
+    for (int d = 0; d < 32; ++d) dst[(size_t)d * vt_ld] = vtile[lane][warp * 32 + d];
+  }
+}
