@@ -196,33 +196,47 @@ __global__ void __launch_bounds__(256) qkv_rope_split_kernel(const bf16* __restr
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const int t0 = blockIdx.x * 32;
   const int pb = pos_base ? *pos_base : 0;
-  for (int i = threadIdx.x; i < 32 * 256; i += 256) {   // pairs of adjacent features
-    const int tl = i >> 8, n = 512 * blockIdx.y + 2 * (i & 255), t = t0 + tl;
-    if (t >= n_tok) continue;
+  // eight threads per token, 64 consecutive features (eight 16-byte vectors) each: all loads of a thread are issued
+  // before the first use, one division per thread
+  const int tl = threadIdx.x >> 3, sub = threadIdx.x & 7, t = t0 + tl;
+  const int nbase = 512 * blockIdx.y + 64 * sub;
+  if (t < n_tok) {
     const int obs = t / rows_per_obs, r = t - obs * rows_per_obs;
-    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(qkv + (size_t)t * 2560 + n);
-    float v0 = __low2float(x), v1 = __high2float(x);
-    if (n < 2304) {
-      const int pos = r + pos_off + pb, fi = (n & 255) >> 1;
-      const float c = rope_cos[pos * 128 + fi], sn = rope_sin[pos * 128 + fi];
-      const float a = v0 * c - v1 * sn, b = v1 * c + v0 * sn;
-      v0 = a; v1 = b;
-    }
-    const __nv_bfloat162 o = __floats2bfloat162_rn(v0, v1);
+    const int pos = r + pos_off + pb;
     const size_t row = (size_t)obs * kv_obs_stride + kv_row_off + r;
-    if (n < 2048) *reinterpret_cast<__nv_bfloat162*>(q + (size_t)t * 2048 + n) = o;
-    else if (n < 2304) *reinterpret_cast<__nv_bfloat162*>(kc + row * 256 + (n - 2048)) = o;
-    else {
-      *reinterpret_cast<__nv_bfloat162*>(vc + row * 256 + (n - 2304)) = o;
-      *reinterpret_cast<__nv_bfloat162*>(&vtile[tl][n - 2304]) = o;
+    uint4 x[8];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) x[g] = *reinterpret_cast<const uint4*>(qkv + (size_t)t * 2560 + nbase + 8 * g);
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      const int n = nbase + 8 * g;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&x[g]);
+      if (n < 2304) {
+        const int fi = (n & 255) >> 1;
+        const float4 c = *reinterpret_cast<const float4*>(rope_cos + pos * 128 + fi);
+        const float4 sn = *reinterpret_cast<const float4*>(rope_sin + pos * 128 + fi);
+        const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float v0 = __low2float(h[k]), v1 = __high2float(h[k]);
+          h[k] = __floats2bfloat162_rn(v0 * cc[k] - v1 * ss[k], v1 * cc[k] + v0 * ss[k]);
+        }
+      }
+      if (n < 2048) *reinterpret_cast<uint4*>(q + (size_t)t * 2048 + n) = x[g];
+      else if (n < 2304) *reinterpret_cast<uint4*>(kc + row * 256 + (n - 2048)) = x[g];
+      else {
+        *reinterpret_cast<uint4*>(vc + row * 256 + (n - 2304)) = x[g];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) *reinterpret_cast<__nv_bfloat162*>(&vtile[tl][n - 2304 + 2 * k]) = h[k];
+      }
     }
   }
   if (!vt || blockIdx.y != 4) return;
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t = t0 + lane;
-  if (t < n_tok) {
-    const int obs = t / rows_per_obs, r = t - obs * rows_per_obs;
+  const int tk = t0 + lane;
+  if (tk < n_tok) {
+    const int obs = tk / rows_per_obs, r = tk - obs * rows_per_obs;
     bf16* dst = vt + ((size_t)obs * 256 + warp * 32) * vt_ld + kv_row_off + r;
 #pragma unroll 8
     for (int d = 0; d < 32; ++d) dst[(size_t)d * vt_ld] = vtile[lane][warp * 32 + d];
