@@ -22,9 +22,9 @@ namespace lk {
 
 constexpr int TILE_FLOATS = 256 * 2048;   // projected tokens of one view (fp32 residual-stream rows)
 constexpr int MAX_VIEWS = 16;
-// trunk mailbox (words): [0, 64) flag per view, [64] forward counter, [65] blocks done, [66] failures;
+// trunk mailbox (words): [0, 64) flag per view, [64] forward counter, [65] blocks done, [66] failures, [67] views;
 // byte 512: unsigned* ack[MAX_VIEWS] (where to acknowledge view v); byte 1024: staging [2][n_views][TILE_FLOATS]
-constexpr int TRUNK_EPOCH = 64, TRUNK_DONE = 65, TRUNK_FAIL = 66;
+constexpr int TRUNK_EPOCH = 64, TRUNK_DONE = 65, TRUNK_FAIL = 66, TRUNK_VIEWS = 67;   // [67]: number of views, set at creation
 constexpr int TRUNK_ACK_OFF = 512, TRUNK_STAGING_OFF = 1024;
 // tower mailbox (words): [0] ack written by the trunk, [16] forward counter, [17] blocks done, [18] failures
 constexpr int TOWER_ACK = 0, TOWER_EPOCH = 16, TOWER_DONE = 17, TOWER_FAIL = 18;

@@ -1560,6 +1560,8 @@ int vla_link_trunk_create(vla_handle m, int n_views, unsigned char* ipc_handle_o
   const size_t bytes = lk::TRUNK_STAGING_OFF + (size_t)2 * n_views * lk::TILE_FLOATS * sizeof(float);
   if (!m->dalloc(&m->link_box, bytes)) return m->fail(VLA_ERR_CUDA, "mailbox allocation failed");
   m->link_views = n_views;
+  // the towers check the view count they were given against this word
+  CK(cudaMemcpy(m->link_box + lk::TRUNK_VIEWS * sizeof(unsigned int), &n_views, sizeof(int), cudaMemcpyHostToDevice));
   return link_export(m, ipc_handle_out, local_ptr_out);
 }
 
@@ -1590,6 +1592,11 @@ int vla_link_tower_connect(vla_handle m, void* trunk_mailbox, int view, int n_vi
   if (m->link_connected) return m->fail(VLA_ERR_STATE, "tower already connected");
   if (view < 0 || view >= n_views || n_views > lk::MAX_VIEWS) return m->fail(VLA_ERR_SHAPE, "view %d of %d", view, n_views);
   cudaSetDevice(m->cfg.device);
+  {
+    int trunk_views = 0;   // the staging slots are laid out for the trunk's view count
+    CK(cudaMemcpy(&trunk_views, reinterpret_cast<const unsigned int*>(trunk_mailbox) + lk::TRUNK_VIEWS, sizeof(int), cudaMemcpyDeviceToHost));
+    if (trunk_views != n_views) return m->fail(VLA_ERR_SHAPE, "the trunk's mailbox was created for %d views, this tower was given %d", trunk_views, n_views);
+  }
   const float4* tile = reinterpret_cast<const float4*>(m->encoder_x);
   float4* staging = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(trunk_mailbox) + lk::TRUNK_STAGING_OFF);
   unsigned int* flags = reinterpret_cast<unsigned int*>(trunk_mailbox);
