@@ -129,6 +129,9 @@ struct Ctx {
   uint32_t sbase;         // shared address of the activation region (1024-aligned)
   uint8_t* sptr;          // generic pointer to the same
   uint32_t w_full, w_empty, a_full, a_empty, att_full, att_full_v;   // att_full: Q and K tiles, att_full_v: V tiles
+  uint32_t umma_bar;      // [8] completion of the GeGLU phase's tcgen05 MMAs, one per weight chunk
+  uint32_t tmem;          // tensor-memory address of the GeGLU accumulator (64 columns)
+  unsigned int umma_n;    // GeGLU phases run so far
   volatile int* go_count; // grid barriers passed, published by thread 0 for the activation warp
   volatile int* s_abort;
   float* fs;              // [64] per-token RMS scale
@@ -616,47 +619,98 @@ __device__ __forceinline__ bool phase_qkv(Ctx& c, int step, int layer) {
 }
 
 // GeGLU: hidden[:, 32c..32c+31] = gelu(f * (xb @ Wg) + bg) * (f * (xb @ Wu) + bu), four (gate, up) tile pairs per CTA.
+// This phase runs on tcgen05: with mma.sync every activation fragment is re-read from shared memory for each group of
+// four feature tiles and the loop sat on the shared-memory bandwidth limit; the tensor core reads both operands
+// straight from the TMA-written tiles, each once.  The CTA's eight weight chunks of the layer are K eighths of all
+// eight tiles ([K block (2)][row (64) = per pair: gate 8 | up 8][128 B, 128-byte swizzle]), so that one accumulator of
+// 64 columns takes the whole phase: lane 0 of warp 2 (a warp without epilogue rows) issues, per 64-wide K block, four
+// MMAs of M = 128 (the 56 token rows of the activation tile; rows 56..127 read whatever lies behind the tile and their
+// results are never looked at) x N = 64 x K = 16 as chunks and activation stages arrive, and commits per chunk; the other
+// warps hand each chunk back when its commit has landed (warp 3 also on the issuer's behalf), and warps 0, 1, 4, 5
+// (TMEM lane quarters 0 and 1 = token rows 0..63, two column halves) run the epilogue with one token row per thread.
 __device__ __forceinline__ bool phase_geglu(Ctx& c, int step, int layer) {
   const Params& p = *c.p;
   if (c.cta >= N_OWNERS) return true;
   bool ok = true;
   XP_MARK(c, 60);
-  const int mi = c.warp & 3, kh = c.warp >> 2;
-  const unsigned long long fv = fs_issue(c);
-#pragma unroll 1
-  for (int pass = 0; pass < 2; ++pass) {     // tiles (gate, up, gate, up) of pairs 2 pass, 2 pass + 1 share the A fragments
-    float bg[2][2] = {{0.f, 0.f}, {0.f, 0.f}}, bu[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-    if (p.pi05 && kh == 0) {
-      const float* g = p.sw_gate + ((size_t)step * p.nl + layer) * 4096;
-      const float* u = p.sw_up + ((size_t)step * p.nl + layer) * 4096;
+  const int qtr = c.warp & 3, half = c.warp >> 2;
+  const int r = 32 * qtr + c.lane;                       // token row of this thread in the epilogue
+  const bool epi = qtr < 2;
+  const uint32_t par = c.umma_n & 1u;
+  ++c.umma_n;
+  if (c.warp == 2) {
+    if (c.lane == 0) {
+      // instruction descriptor: D = f32, A = B = bf16, both K-major, N = 64, M = 128
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | (8u << 24);
+      int j = 0;
+      for (; j < 8; ++j) {
+        const uint32_t slot = acquire_chunk(c, c.chunk_g + j, &ok);
+        if ((j & 1) == 0 && !a_wait(c, c.a_g + (j >> 1))) ok = false;
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t stage = c.sbase + (uint32_t)((c.a_g + (j >> 1)) & 3u) * STAGE_BYTES;
 #pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        const int n = 32 * c.cta + 8 * (2 * pass + q) + 2 * (c.lane & 3);
-        bg[q][0] = g[n]; bg[q][1] = g[n + 1]; bu[q][0] = u[n]; bu[q][1] = u[n + 1];
-      }
-    }
-    float acc[4][4];
-    mma_resident<4, true>(c, nullptr, p.S, c.a_g, acc, &ok, c.chunk_g);   // waits for and hands back its chunks quarter by quarter
-    c.chunk_g += 4;
-    if (pass == 0) fs_finish(c, fv);
-    reduce_khalves<4>(c, pass == 1, acc);   // the barrier inside also publishes fs
-    XP_MARK(c, 61 + pass);
-    if (kh == 0) {
+        for (int kb = 0; kb < 2; ++kb) {
+          const uint64_t da = attn_desc_sw128(stage + (2 * (j & 1) + kb) * TILE_BYTES), db = attn_desc_sw128(slot + kb * 8192);
 #pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        const int n = 32 * c.cta + 8 * (2 * pass + q) + 2 * (c.lane & 3);
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int r = 16 * mi + (c.lane >> 2) + 8 * h;
-          if (r >= p.S) continue;
-          const float f = c.fs[r];
-          const float h0 = gelu_tanh_f(f * acc[2 * q][2 * h] + bg[q][0]) * (f * acc[2 * q + 1][2 * h] + bu[q][0]);
-          const float h1 = gelu_tanh_f(f * acc[2 * q][2 * h + 1] + bg[q][1]) * (f * acc[2 * q + 1][2 * h + 1] + bu[q][1]);
-          *reinterpret_cast<uint32_t*>(p.hidden + (size_t)r * 4096 + n) = pack_bf16x2(h0, h1);
+          for (int kk = 0; kk < 4; ++kk) umma_bf16(c.tmem, da + 2 * kk, db + 2 * kk, idesc, (j | kb | kk) != 0 ? 1u : 0u);
         }
+        umma_commit(c.umma_bar + 8 * j);   // this chunk has been read once its MMAs complete: the ring refills during the phase
+      }
+      // after a failed wait the remaining commits are still made: the other warps are released and see the abort flag
+      for (int k = j; k < 8; ++k) umma_commit(c.umma_bar + 8 * k);
+      // the issuing lane never waits for a commit (that would tie the issue of a chunk to the completion of the one
+      // before it); warp 3 hands the chunks back on this warp's behalf
+    }
+    __syncwarp();
+  } else {
+    // the per-token scale of this thread's row, straight from the sums of squares (no exchange through shared memory)
+    unsigned long long ssq = 0ull;
+    if (epi && r < p.S) ssq = __ldcg(p.ssq + ((c.pk + 2u) % 3u) * 64 + r);
+    float bg[2][8], bu[2][8];
+#pragma unroll
+    for (int q = 0; q < 2; ++q)
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { bg[q][k] = 0.f; bu[q][k] = 0.f; }
+    const int n0 = 32 * c.cta + 16 * half;               // first of this thread's sixteen hidden features (two tile pairs)
+    if (p.pi05 && epi) {
+      const float* g = p.sw_gate + ((size_t)step * p.nl + layer) * 4096 + n0;
+      const float* u = p.sw_up + ((size_t)step * p.nl + layer) * 4096 + n0;
+#pragma unroll
+      for (int q = 0; q < 2; ++q)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { bg[q][k] = g[8 * q + k]; bu[q][k] = u[8 * q + k]; }
+    }
+    for (int j = 0; j < 8; ++j) {
+      if (!wait_bar(c, c.umma_bar + 8 * j, par)) ok = false;
+      release_chunk(c, c.chunk_g + j);
+      if (c.warp == 3 && c.lane == 0) mbar_arrive(c.w_empty + 8 * ((c.chunk_g + j) % NSLOT));   // for the issuing warp
+    }
+    tc_fence_after();
+    XP_MARK(c, 61);
+    if (epi) {
+      uint32_t v[32];
+      tmem_ld32(c.tmem + ((uint32_t)(32 * qtr) << 16) + 32 * half, v);   // pairs 2 half, 2 half + 1: gate 8 | up 8 each
+      tmem_ld_wait();
+      if (r < p.S && ok) {
+        const float f = rsqrtf((float)ssq * (1.0f / (SSQ_FIX * 1024.0f)) + 1e-6f);
+        uint32_t o[8];
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float h0 = gelu_tanh_f(f * __uint_as_float(v[16 * q + 2 * k]) + bg[q][2 * k]) * (f * __uint_as_float(v[16 * q + 8 + 2 * k]) + bu[q][2 * k]);
+            const float h1 = gelu_tanh_f(f * __uint_as_float(v[16 * q + 2 * k + 1]) + bg[q][2 * k + 1]) * (f * __uint_as_float(v[16 * q + 9 + 2 * k]) + bu[q][2 * k + 1]);
+            o[4 * q + k] = pack_bf16x2(h0, h1);
+          }
+        uint4* dst = reinterpret_cast<uint4*>(p.hidden + (size_t)r * 4096 + n0);
+        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
       }
     }
   }
+  c.chunk_g += 8;
+  tc_fence_before();
   a_release4(c);
   XP_MARK(c, 65);
   return ok;
@@ -1106,6 +1160,8 @@ __global__ void __launch_bounds__(THREADS, 1) expert_persistent_kernel(const __g
   c.a_empty = c.a_full + 8 * N_ASTAGE;
   c.att_full = c.a_empty + 8 * N_ASTAGE;
   c.att_full_v = c.att_full + 8;
+  c.umma_bar = c.att_full_v + 8;
+  c.umma_n = 0;
   c.go_count = reinterpret_cast<volatile int*>(persist + 256);
   c.s_abort = reinterpret_cast<volatile int*>(persist + 260);
   c.fs = reinterpret_cast<float*>(persist + 512);
@@ -1136,6 +1192,7 @@ __global__ void __launch_bounds__(THREADS, 1) expert_persistent_kernel(const __g
     }
     mbar_init(c.att_full, 1);
     mbar_init(c.att_full_v, 1);
+    for (int j = 0; j < 8; ++j) mbar_init(c.umma_bar + 8 * j, 1);
     *c.go_count = 0;
     *c.s_abort = 0;
     mbar_fence_init();
@@ -1151,12 +1208,17 @@ __global__ void __launch_bounds__(THREADS, 1) expert_persistent_kernel(const __g
     }
     c.rope[i] = v;
   }
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(persist + 264);   // behind the mbarriers (25 x 8 bytes) and the two words at 256
+  if (c.warp == 0) tmem_alloc(smem_u32(tmem_slot), 64);   // GeGLU accumulator
   if (threadIdx.x == 32 * 9) {
     tma_prefetch_desc(&p.tm_xb); tma_prefetch_desc(&p.tm_attn); tma_prefetch_desc(&p.tm_hidden);
     tma_prefetch_desc(&p.tm_q); tma_prefetch_desc(&p.tm_k); tma_prefetch_desc(&p.tm_v);
     if (!p.pi05) tma_prefetch_desc(&p.tm_act);
   }
+  tc_fence_before();
   __syncthreads();
+  tc_fence_after();
+  c.tmem = *tmem_slot;
 
   if (c.warp == 8) {
     if (c.lane == 0) weight_producer_loop(c);
@@ -1216,7 +1278,9 @@ __global__ void __launch_bounds__(THREADS, 1) expert_persistent_kernel(const __g
     c.fine = false;
     if (!ok) *c.s_abort = 1;
   }
+  tc_fence_before();
   __syncthreads();
+  if (c.warp == 0) tmem_dealloc(c.tmem, 64);
 }
 
 // ---- weight packing ----------------------------------------------------------------------------------------------------------
@@ -1249,17 +1313,18 @@ __global__ void pack_layer_kernel(const bf16* __restrict__ w_qkv, const bf16* __
   const int j = blockIdx.x, cta = blockIdx.y, G = gridDim.y;
   bf16* dst = stream + ((size_t)cta * chunks_per_cta + (size_t)layer * CH_PER_LAYER + j) * (CHUNK_BYTES / 2);
   if (j >= 5 && j < 13) {
-    // MLP gate/up: pass p = (j - 5) / 4 covers the (gate, up) pairs 2p, 2p + 1 of this CTA's 32 hidden features; the chunk
-    // holds K quarter q of the pass's four tiles (gate, up, gate, up): [tile][k-step pair (8)][lane][8 bf16].
-    // Stream order of the quarters within a pass: q0, q2, q1, q3.
+    // MLP gate/up: chunk j - 5 holds K eighth j - 5 (128 K = two 64-wide K blocks) of this CTA's 32 hidden features as
+    // the B operand of the tcgen05 MMAs: [K block (2)][row (64)][128 B], row = 16 pair + (gate 0..7 | up 8..15), the
+    // 16-byte chunks of a row permuted by the 128-byte swizzle (logical chunk c of row r at c ^ (r & 7)).
     if (cta >= N_OWNERS) return;
-    const int pass = (j - 5) >> 2, oi = (j - 5) & 3, q = ((oi & 1) << 1) | (oi >> 1);
+    const int k8 = j - 5;
     for (int e = threadIdx.x; e < CHUNK_BYTES / 2; e += blockDim.x) {
-      const int jj = e & 7, lane = (e >> 3) & 31, spq = (e >> 8) & 7, t = e >> 11;
-      const int ks = 2 * spq + (jj >> 2);                                      // k16 step within the quarter
-      const int k = 256 * q + 16 * ks + 8 * ((jj & 3) >> 1) + 2 * (lane & 3) + (jj & 1);
-      const int n = 32 * cta + 8 * (2 * pass + (t >> 1)) + (lane >> 2);
-      dst[e] = ((t & 1) ? w_up : w_gate)[(size_t)n * 1024 + k];
+      const int kb = e >> 12, row = (e >> 6) & 63, pc = (e >> 3) & 7, w8 = e & 7;   // physical 16-byte chunk pc of the row
+      const int ch = pc ^ (row & 7);                                             // logical chunk stored there
+      const int k = 128 * k8 + 64 * kb + 8 * ch + w8;
+      const int pair = row >> 4, up = (row >> 3) & 1;
+      const int n = 32 * cta + 8 * pair + (row & 7);
+      dst[e] = (up ? w_up : w_gate)[(size_t)n * 1024 + k];
     }
     return;
   }
