@@ -53,7 +53,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # 788 tokens, and the persistent action-expert kernel (captured at reduced depth, scaled to 18 layers x 10 steps by
 # the layer-steps processed: its traffic is the weight stream, which grows in proportion).
 NCU_TRAFFIC_GEGLU = {"cfg2": 144519168}
-NCU_TRAFFIC_EXPERT = {"any": int(353.1e6 * 18)}
+NCU_TRAFFIC_EXPERT = {"any": int(354.1e6 * 18)}
 
 
 def peaks():
