@@ -8,6 +8,9 @@
 //     mma B-fragment order) in exactly the order the CTA consumes them; warp 8 copies the stream into a ring of shared
 //     memory slots with cp.async.bulk, decoupled from the phase structure: while the CTA waits at a grid barrier the
 //     weights of the next operators keep arriving from HBM.
+//   * the GeGLU phase runs on tcgen05 instead: its chunks are K eighths of all eight (gate, up) tiles in the K-major,
+//     128-byte-swizzled operand layout, the accumulator (128 x 64 fp32) lives in tensor memory, one lane issues the
+//     MMAs on the TMA-written activation tiles and the epilogue reads one token row per thread (see phase_geglu).
 //   * activations are small (<= 56 x 4096 bf16) and live in L2; warp 9 brings them in with TMA (cp.async.bulk.tensor,
 //     128-byte swizzle, 64-wide K blocks) through a ring of four 256-wide K stages as soon as the grid barrier before
 //     the phase is passed; the MMA warps read them with ldmatrix.
@@ -41,7 +44,7 @@ constexpr int PERSIST_BYTES = 10240;          // barriers, per-token scales, thi
 constexpr int SMEM_BYTES = PERSIST_OFF + PERSIST_BYTES + 1024;   // + slack to align the base to 1024 B
 constexpr float SSQ_FIX = 16777216.0f;   // sums of squares travel as 40.24 fixed point: integer adds are order independent
 constexpr int N_OWNERS = 128;         // CTAs that own 8 features of the 1024-wide stream / 32 hidden features
-constexpr int CH_PER_LAYER = 17;      // stream slots per layer: qkv 0-2, o 3-4, (gate,up) x4 5-12, down 13-16
+constexpr int CH_PER_LAYER = 17;      // stream slots per layer: qkv 0-2, o 3-4, gate/up K eighths 5-12, down 13-16
 constexpr int ATT_ROWS = 32;          // query rows per attention work item
 constexpr int ATT_MAX_KEYS = 96;      // keys per split
 constexpr int MRG_BATCH = 12;         // key splits merged per round of loads
@@ -268,14 +271,9 @@ __device__ __forceinline__ void ssq_add(const Ctx& c, int token, float sq) {
 // NT feature tiles (their chunks at slot addresses sl[0..NT-1]) against the four activation stages a_g0..a_g0+3 (K = 1024);
 // warp (mi, kh) takes rows 16 mi.. and K half kh.  The loop is bound by shared-memory bandwidth (1 KB of A and NT x 512 B
 // of B per iteration and warp), so the more tiles share an A fragment the better.
-// QUARTERS (GeGLU, NT = 4): the four chunks of a pass are K quarters [4 tiles][8 k-step pairs][lane][16 B] in the stream
-// order q0, q2, q1, q3 (the two K halves are read concurrently by the kh = 0 and kh = 1 warps), and every warp hands a
-// pair of quarters back as soon as it is through its own, so that the weight stream refills the ring during the pass
-// instead of after it.  chunk_g0 = index of the first chunk of the pass.
-template <int NT, bool QUARTERS = false>
+template <int NT>
 __device__ __forceinline__ void mma_resident(Ctx& c, const uint32_t* sl, int rows, unsigned int a_g0, float (&acc)[NT][4], bool* ok,
-                                             unsigned int chunk_g0 = 0, int nt = NT) {
-  static_assert(!QUARTERS || NT == 4, "the quarter layout holds four tiles per chunk");
+                                             int nt = NT) {
   const int mi = c.warp & 3, kh = c.warp >> 2;
   float acc2[4] = {0.f, 0.f, 0.f, 0.f};   // a single tile alternates two accumulators to break the dependent chain
 #pragma unroll
@@ -285,16 +283,11 @@ __device__ __forceinline__ void mma_resident(Ctx& c, const uint32_t* sl, int row
   // every warp waits for the stages of its K half, also a warp without rows: the stages are then handed back in step
   if (!a_wait(c, a_g0 + 2 * kh) || !a_wait(c, a_g0 + 2 * kh + 1)) *ok = false;
   XP_MARK(c, 90);
-  if (16 * mi >= rows || !*ok) {
-    if (QUARTERS)
-      for (int j = 0; j < 4; ++j) release_chunk(c, chunk_g0 + j);
-    return;
-  }
+  if (16 * mi >= rows || !*ok) return;
   const int row = min(16 * mi + (c.lane & 15), rows - 1);
   const int hi = c.lane >> 4;
   const uint32_t lane_off = (uint32_t)c.lane * 16;
   const uint32_t a_off0 = swz128(row, hi), a_off1 = swz128(row, hi + 2), a_off2 = swz128(row, hi + 4), a_off3 = swz128(row, hi + 6);
-  uint32_t qchunk = 0;
 #pragma unroll 2
   for (int i = 0; i < 8; ++i) {          // one 64-wide K block (four k16 steps) per round
     const int kb = 8 * kh + i;
@@ -304,16 +297,10 @@ __device__ __forceinline__ void mma_resident(Ctx& c, const uint32_t* sl, int row
     ldsm_x4(tile + a_off1, a[4], a[5], a[6], a[7]);
     ldsm_x4(tile + a_off2, a[8], a[9], a[10], a[11]);
     ldsm_x4(tile + a_off3, a[12], a[13], a[14], a[15]);
-    // quarter q = kb / 4 is chunk ((q & 1) << 1) | (q >> 1) of the pass; it is waited for only when this warp gets to it
-    uint32_t qbase = 0;
-    if (QUARTERS) {
-      if ((i & 3) == 0) qchunk = acquire_chunk(c, chunk_g0 + ((kb >> 2) & 1) * 2 + (kb >> 3), ok);
-      qbase = qchunk + (uint32_t)((2 * kb) & 7) * 512 + lane_off;
-    }
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
       if (t >= nt) break;                // fewer tiles than NT: the same in every thread
-      const uint32_t baddr = QUARTERS ? qbase + (uint32_t)t * 4096 : sl[t] + (uint32_t)(2 * kb) * 512 + lane_off;
+      const uint32_t baddr = sl[t] + (uint32_t)(2 * kb) * 512 + lane_off;
       const uint4 b0 = lds128(baddr);
       const uint4 b1 = lds128(baddr + 512);
       float* second = NT == 1 ? acc2 : acc[t];
@@ -321,10 +308,6 @@ __device__ __forceinline__ void mma_resident(Ctx& c, const uint32_t* sl, int row
       mma16816(second, a[4], a[5], a[6], a[7], b0.z, b0.w);
       mma16816(acc[t], a[8], a[9], a[10], a[11], b1.x, b1.y);
       mma16816(second, a[12], a[13], a[14], a[15], b1.z, b1.w);
-    }
-    if (QUARTERS && (i & 3) == 3) {      // through a quarter: hand back the pair of quarters the two K halves just finished
-      release_chunk(c, chunk_g0 + (i >> 2) * 2);
-      release_chunk(c, chunk_g0 + (i >> 2) * 2 + 1);
     }
   }
   if (NT == 1) {
@@ -583,7 +566,7 @@ __device__ __forceinline__ bool phase_qkv(Ctx& c, int step, int layer) {
   for (int j = 0; j < NQ; ++j) sl[j] = j < nq ? acquire_chunk(c, c.chunk_g + j, &ok) : 0u;
   XP_MARK(c, 1);
   float acc[NQ][4];
-  mma_resident<NQ>(c, sl, p.S, c.a_g, acc, &ok, 0, nq);
+  mma_resident<NQ>(c, sl, p.S, c.a_g, acc, &ok, nq);
   XP_MARK(c, 2);
 #pragma unroll
   for (int j = 0; j < NQ; ++j)
@@ -1305,7 +1288,7 @@ __global__ void pack_chunk_kernel(const bf16* __restrict__ w, int Kp, int n_vali
 // All chunks of one expert layer: grid (CH_PER_LAYER, G).  Stream slot j of CTA c holds (K-major sources, layer l):
 //   j = 0..2   QKV feature tile c + j G (if < 320), K 0..1023
 //   j = 3..4   attention-out tile c, K half j - 3                      (c < N_OWNERS from here on)
-//   j = 5..12  MLP gate / up in K quarters (see below)
+//   j = 5..12  MLP gate / up: K eighth j - 5 of all eight tiles as a tcgen05 operand (see below)
 //   j = 13..16 MLP down tile c, K quarter j - 13
 __global__ void pack_layer_kernel(const bf16* __restrict__ w_qkv, const bf16* __restrict__ w_o, const bf16* __restrict__ w_gate,
                                   const bf16* __restrict__ w_up, const bf16* __restrict__ w_down, int layer, int chunks_per_cta,
